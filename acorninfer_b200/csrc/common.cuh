@@ -1,0 +1,79 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions.
+//
+// Every entry point is extern "C", takes raw device pointers, sizes and a stream,
+// launches on that stream and returns the cudaError_t of the launch as int
+// (0 = success).  Element type is chosen by a dtype code: 0 = float32, 1 = bfloat16.
+// Argument validation (sizes a kernel supports, alignment) is done by the Python
+// wrappers before the call; a kernel refuses what it cannot compute with
+// ACORN_ERR_UNSUPPORTED rather than computing something else.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define ACORN_DTYPE_F32 0
+#define ACORN_DTYPE_BF16 1
+#define ACORN_ERR_UNSUPPORTED 10001
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; `scratch` holds at least 32 floats of shared memory.  All threads
+// of the block must call it; every thread receives the total.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}
+
+#define ACORN_DISPATCH_DTYPE(dtype, T, ...)                    \
+    do {                                                       \
+        if ((dtype) == ACORN_DTYPE_F32) {                      \
+            typedef float T;                                   \
+            __VA_ARGS__;                                       \
+        } else if ((dtype) == ACORN_DTYPE_BF16) {              \
+            typedef bf16 T;                                    \
+            __VA_ARGS__;                                       \
+        } else {                                               \
+            return ACORN_ERR_UNSUPPORTED;                      \
+        }                                                      \
+    } while (0)
+
+static inline int acorn_launch_status() { return (int)cudaGetLastError(); }

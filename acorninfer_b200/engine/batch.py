@@ -1,0 +1,256 @@
+"""One step's batch: what the caller gives, and the arrays the kernels read.
+
+A step is a list of :class:`StepEntry`: a request (its :class:`RequestCache`), its next
+tokens, and the places among them whose logits are wanted.  All entries of a step form
+one flat token batch; an entry is a *row*.  ``plan_step`` lays the batch out as plain
+integer arrays (host side, no device needed); ``StepWorkspace`` packs them into one
+pinned staging block and copies it to the device in a single transfer.
+
+Arrays (int32), T tokens, R rows, W wanted logits, per cache group g:
+  token_ids[T], positions[T] (absolute index of the token in its request),
+  token_row[T], row_start[R+1] (offsets into the token arrays), row_pos[R] (tokens of
+  the request in the cache before this step), row_slot[R], logit_tokens[W],
+  g.kv_len[R] (row_pos + the row's tokens), g.page_base[R], g.block_table[R, stride].
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from ..cache.manager import CacheManager, RequestCache
+
+
+class BatchError(ValueError):
+    """A step that cannot run as given; nothing was launched or allocated."""
+
+
+@dataclass
+class StepEntry:
+    cache: RequestCache
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+@dataclass
+class GroupPlan:
+    kv_len: np.ndarray
+    page_base: np.ndarray
+    block_table: np.ndarray     # [R, stride]
+    max_kv_len: int
+
+
+@dataclass
+class StepPlan:
+    """Host-side description of a step (numpy int32 arrays)."""
+
+    num_tokens: int
+    num_rows: int
+    token_ids: np.ndarray
+    positions: np.ndarray
+    token_row: np.ndarray
+    row_start: np.ndarray
+    row_pos: np.ndarray
+    row_slot: np.ndarray
+    logit_tokens: np.ndarray
+    groups: list[GroupPlan]
+    row_lens: list[int]
+    max_q_len: int
+    all_decode: bool            # every row is a single token
+
+    @property
+    def num_logits(self) -> int:
+        return int(self.logit_tokens.size)
+
+
+def _table_stride(pages: int) -> int:
+    """Block-table row stride: a power of two >= 8, so few distinct strides occur over a run."""
+    stride = 8
+    while stride < pages:
+        stride *= 2
+    return stride
+
+
+def validate_entries(entries: list[StepEntry], vocab_size: int, max_tokens: int | None = None) -> None:
+    if not entries:
+        raise BatchError("a step needs at least one entry")
+    seen = set()
+    total = 0
+    for e in entries:
+        rid = e.cache.request_id
+        if e.cache.closed:
+            raise BatchError(f"request {rid!r} is closed")
+        if id(e.cache) in seen:
+            raise BatchError(f"request {rid!r} appears twice in one step")
+        seen.add(id(e.cache))
+        if len(e.tokens) < 1:
+            raise BatchError(f"request {rid!r} brings no tokens")
+        for t in e.tokens:
+            if not (0 <= int(t) < vocab_size):
+                raise BatchError(f"request {rid!r}: token id {t} outside the vocabulary (0..{vocab_size - 1})")
+        for w in e.want:
+            if not (0 <= int(w) < len(e.tokens)):
+                raise BatchError(f"request {rid!r}: wanted place {w} outside its {len(e.tokens)} tokens")
+        total += len(e.tokens)
+    if max_tokens is not None and total > max_tokens:
+        raise BatchError(f"step has {total} tokens, the workspace holds {max_tokens}")
+
+
+def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
+    """Lays out a validated step whose pages are already reserved (``manager.extend`` done)."""
+    R = len(entries)
+    lens = [len(e.tokens) for e in entries]
+    T = sum(lens)
+    token_ids = np.empty(T, np.int32)
+    positions = np.empty(T, np.int32)
+    token_row = np.empty(T, np.int32)
+    row_start = np.zeros(R + 1, np.int32)
+    row_pos = np.empty(R, np.int32)
+    row_slot = np.empty(R, np.int32)
+    logit_tokens: list[int] = []
+    off = 0
+    for r, e in enumerate(entries):
+        n = lens[r]
+        token_ids[off:off + n] = e.tokens
+        positions[off:off + n] = np.arange(e.cache.length, e.cache.length + n, dtype=np.int32)
+        token_row[off:off + n] = r
+        row_pos[r] = e.cache.length
+        row_slot[r] = e.cache.slot
+        logit_tokens.extend(off + int(w) for w in e.want)
+        off += n
+        row_start[r + 1] = off
+    groups = []
+    P = manager.page_size
+    for g in manager.groups:
+        tables = [e.cache.tables[g.index] for e in entries]
+        stride = _table_stride(max((len(t) for t in tables), default=0))
+        bt = np.zeros((R, stride), np.int32)
+        kv_len = np.empty(R, np.int32)
+        base = np.empty(R, np.int32)
+        for r, e in enumerate(entries):
+            t = tables[r]
+            new_len = e.cache.length + lens[r]
+            if (e.cache.page_base[g.index] + len(t)) * P < new_len:
+                raise BatchError(f"request {e.cache.request_id!r}: pages of group {g.index} do not cover length {new_len}")
+            bt[r, :len(t)] = t
+            kv_len[r] = new_len
+            base[r] = e.cache.page_base[g.index]
+        groups.append(GroupPlan(kv_len, base, bt, int(kv_len.max()) if R else 0))
+    return StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
+                    np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens))
+
+
+# --------------------------------------------------------------------------- device side
+
+
+@dataclass
+class GroupInputs:
+    kv_len: object
+    page_base: object
+    block_table: object         # [R, stride] view
+    max_kv_len: int
+
+
+@dataclass
+class StepInputs:
+    """Device views of a step's arrays, plus the host-side facts launches need."""
+
+    num_tokens: int
+    num_rows: int
+    token_ids: object
+    positions: object
+    token_row: object
+    row_start: object
+    row_pos: object
+    row_slot: object
+    logit_tokens: object
+    groups: list[GroupInputs]
+    plan: StepPlan
+    scratch: dict = field(default_factory=dict)     # per-step products shared by parts (e.g. split plans)
+
+    @property
+    def num_logits(self) -> int:
+        return self.plan.num_logits
+
+
+class StepWorkspace:
+    """Pinned staging blocks and a device block that a step's arrays are packed into.
+
+    The layout is a function of (T, R, W, strides) only, so two steps of the same shape
+    put every array at the same device address: a captured CUDA graph of one can be
+    replayed for the other after ``upload``.
+    """
+
+    def __init__(self, device, capacity_ints: int = 1 << 20, num_staging: int = 3):
+        import torch
+        self.torch = torch
+        self.device = device
+        self.capacity = capacity_ints
+        self.device_block = torch.zeros(capacity_ints, dtype=torch.int32, device=device)
+        self.staging = [torch.zeros(capacity_ints, dtype=torch.int32).pin_memory() for _ in range(num_staging)]
+        self.events = [None] * num_staging
+        self._next = 0
+
+    @staticmethod
+    def layout(plan: StepPlan) -> tuple[dict, int]:
+        """Offsets (in int32 elements, 4-aligned) of every array in the block."""
+        off = 0
+        out = {}
+
+        def put(name, n):
+            nonlocal off
+            out[name] = (off, n)
+            off += (n + 3) // 4 * 4
+
+        T, R = plan.num_tokens, plan.num_rows
+        put("token_ids", T)
+        put("positions", T)
+        put("token_row", T)
+        put("row_start", R + 1)
+        put("row_pos", R)
+        put("row_slot", R)
+        put("logit_tokens", plan.num_logits)
+        for i, g in enumerate(plan.groups):
+            put(f"g{i}.kv_len", R)
+            put(f"g{i}.page_base", R)
+            put(f"g{i}.block_table", g.block_table.size)
+        return out, off
+
+    def upload(self, plan: StepPlan) -> StepInputs:
+        torch = self.torch
+        lay, total = self.layout(plan)
+        if total > self.capacity:
+            raise BatchError(f"step arrays need {total} ints, workspace holds {self.capacity}")
+        i = self._next
+        self._next = (self._next + 1) % len(self.staging)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        host = self.staging[i].numpy()
+        arrays = {
+            "token_ids": plan.token_ids, "positions": plan.positions, "token_row": plan.token_row,
+            "row_start": plan.row_start, "row_pos": plan.row_pos, "row_slot": plan.row_slot,
+            "logit_tokens": plan.logit_tokens,
+        }
+        for gi, g in enumerate(plan.groups):
+            arrays[f"g{gi}.kv_len"] = g.kv_len
+            arrays[f"g{gi}.page_base"] = g.page_base
+            arrays[f"g{gi}.block_table"] = g.block_table.reshape(-1)
+        for name, arr in arrays.items():
+            off, n = lay[name]
+            host[off:off + n] = arr
+        self.device_block[:total].copy_(self.staging[i][:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+        def view(name):
+            off, n = lay[name]
+            return self.device_block[off:off + n]
+
+        groups = []
+        for gi, g in enumerate(plan.groups):
+            bt = view(f"g{gi}.block_table").view(plan.num_rows, g.block_table.shape[1])
+            groups.append(GroupInputs(view(f"g{gi}.kv_len"), view(f"g{gi}.page_base"), bt, g.max_kv_len))
+        return StepInputs(plan.num_tokens, plan.num_rows, view("token_ids"), view("positions"), view("token_row"),
+                          view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan)

@@ -1,0 +1,119 @@
+"""The step function: one batch of (request, its next tokens) -> logits at the wanted places.
+
+``ModelRunner`` owns the model, the cache manager and the step workspace.  ``step``
+  1. validates the batch on the host (a bad batch raises; nothing ran, nothing is held),
+  2. reserves the pages the step writes (all requests or none: ``PoolExhausted``),
+  3. lays the batch out and uploads it in one transfer,
+  4. runs the model over exactly the tokens given, reading earlier tokens from the cache,
+  5. commits the new lengths (windowed groups give pages back),
+and returns float32 logits ``[wanted, vocab]`` in the order of the entries and their
+``want`` lists.  Prompt portions and single decoded tokens are the same code path; how the
+tokens were cut into steps, what else is in the batch and which pages hold them change the
+result by rounding only.  Generation, replay and the benchmark all go through here.
+
+Reference: the reference runs a scheduled step as up to four forwards
+(``acorninfer/engine/engine.py:167-262``, ``acorninfer/engine/executor.py:21-108``);
+here it is one forward over the flat token batch.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..cache.pools import PoolExhausted
+from ..config.model_config import ModelConfig
+from ..kernels import ops
+from ..models.decoder import Decoder
+from ..registry import load_config, spec_for
+from ..weights.loader import load_tensors
+from ..weights.random_init import random_state
+from .batch import BatchError, StepEntry, StepWorkspace, plan_step, validate_entries
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class ModelRunner:
+    def __init__(self, config: ModelConfig, tensors: dict[str, torch.Tensor] | None, *, dtype: str = "bfloat16",
+                 device: str = "cuda:0", num_blocks: int = 1024, page_size: int = 16, max_requests: int = 64,
+                 max_step_tokens: int = 8192, decoder: Decoder | None = None):
+        ops.lib()      # fails here, loudly, if there is no device or no compiled kernels
+        self.config = config
+        self.dtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.spec = spec_for(config)
+        self.decoder = decoder or Decoder(self.spec, self.dtype, self.device, page_size)
+        if tensors is not None:
+            self.decoder.bind(tensors)
+        kv_needs, state_needs = self.decoder.cache_needs()
+        self.manager = CacheManager(kv_needs, state_needs, num_blocks, page_size, max_requests,
+                                    dtype=self.dtype, device=self.device)
+        self.caches = self.decoder.entry_caches(self.manager)
+        self.max_step_tokens = max_step_tokens
+        self.workspace = StepWorkspace(self.device)
+        self.vocab_size = self.spec.vocab_size
+
+    # ------------------------------------------------------------------ construction
+
+    @classmethod
+    def from_model_dir(cls, model_dir: str | Path, **kw) -> "ModelRunner":
+        config = load_config(model_dir)
+        dtype = kw.get("dtype", "bfloat16")
+        tdtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
+        device = kw.get("device", "cuda:0")
+        probe = Decoder(spec_for(config), tdtype, device, kw.get("page_size", 16))
+        tensors = load_tensors(model_dir, probe.expected_tensors(), tdtype, device, probe.ignorable_tensors())
+        probe.bind(tensors)
+        return cls(config, None, decoder=probe, **kw)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig, seed: int, sigma: float = 0.02, sigma_norm: float = 0.0,
+                    **kw) -> "ModelRunner":
+        """Random weights drawn straight on the device (no folder): for benchmarks of large sizes."""
+        dtype = kw.get("dtype", "bfloat16")
+        tdtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
+        device = kw.get("device", "cuda:0")
+        probe = Decoder(spec_for(config), tdtype, device, kw.get("page_size", 16))
+        tensors = random_state(probe.expected_tensors(), seed, sigma, sigma_norm, torch.bfloat16, device)
+        if tdtype == torch.float32:
+            tensors = {k: v.float() for k, v in tensors.items()}
+        probe.bind(tensors)
+        del tensors
+        return cls(config, None, decoder=probe, **kw)
+
+    # ------------------------------------------------------------------ requests
+
+    def open(self, request_id) -> RequestCache:
+        return self.manager.open(request_id)
+
+    def close(self, cache: RequestCache) -> None:
+        self.manager.close(cache)
+
+    # ------------------------------------------------------------------ the step
+
+    def reserve(self, entries: list[StepEntry]) -> None:
+        """Pages for every entry of the step, or for none of them."""
+        need = [0] * len(self.manager.groups)
+        for e in entries:
+            for gi, n in enumerate(self.manager.pages_needed(e.cache, e.cache.length + len(e.tokens))):
+                need[gi] += n
+        free = self.manager.free_pages()
+        for gi, (n, f) in enumerate(zip(need, free)):
+            if n > f:
+                raise PoolExhausted(f"step needs {n} page(s) in cache group {gi}, {f} free")
+        for e in entries:
+            self.manager.extend(e.cache, e.cache.length + len(e.tokens))
+
+    @torch.inference_mode()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        validate_entries(entries, self.vocab_size, self.max_step_tokens)
+        self.reserve(entries)
+        plan = plan_step(entries, self.manager)
+        inputs = self.workspace.upload(plan)
+        logits = self.decoder.forward(inputs, self.caches)
+        for e in entries:
+            self.manager.commit(e.cache, e.cache.length + len(e.tokens))
+        return logits

@@ -1,0 +1,310 @@
+"""Python faces of the CUDA kernels: argument checks, then one launch on the current stream.
+
+The shared library is loaded with ctypes on first use (compiled first if stale).
+Every wrapper checks dtype, device, contiguity and the sizes the kernel supports and
+raises ``KernelError`` for what it cannot compute; there is no other implementation
+to fall back to.  Tensors are passed as raw device pointers.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from .build import ensure_built
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+F32, BF16 = 0, 1
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not torch.cuda.is_available():
+            raise KernelError("acorninfer_b200 needs a CUDA device (sm_100a); none is visible and there is no CPU path")
+        path = ensure_built()
+        _lib = ctypes.CDLL(str(path))
+        for name in dir(_Sigs):
+            if name.startswith("acorn_"):
+                fn = getattr(_lib, name, None)
+                if fn is None:
+                    raise KernelError(f"{path} lacks the symbol {name}: stale build?")
+                fn.argtypes = getattr(_Sigs, name)
+                fn.restype = c_int
+        _lib.acorn_uniform.restype = c_float
+    return _lib
+
+
+class _Sigs:
+    acorn_embed = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_add_rmsnorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
+    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_cast = [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+    acorn_qk_rope_kv = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                        c_int, c_void_p]
+    acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                             c_void_p]
+    acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
+    acorn_sample = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_void_p, c_void_p]
+    acorn_uniform = [ctypes.c_uint64, ctypes.c_uint64]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, dims: int | None = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, got shape {tuple(t.shape)}")
+
+
+def _ok(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == 10001:
+        raise KernelError(f"{what}: sizes or dtypes not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+# ------------------------------------------------------------------ elementwise / norm
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out32: torch.Tensor | None = None) -> torch.Tensor:
+    """out32[t] = table[ids[t]] as float32.  ids int32 [T]; table [V, H]."""
+    _check(ids, "ids", torch.int32, 1)
+    _check(table, "table", None, 2)
+    T, H = ids.numel(), table.shape[1]
+    if out32 is None:
+        out32 = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(out32, "out32", torch.float32, 2)
+    _ok(lib().acorn_embed(ids.data_ptr(), table.data_ptr(), out32.data_ptr(), T, H, dtype_code(table.dtype),
+                          _stream()), "embed")
+    return out32
+
+
+def add_rmsnorm(resid32: torch.Tensor, delta: torch.Tensor | None, weight32: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, row_idx: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """resid32 += delta (in place, unless row_idx is given); returns rmsnorm(resid32) * weight.
+
+    With ``row_idx`` (int32 [R]) only those rows are normed, into rows 0..R-1 of the result,
+    and the residual is left as it is.
+    """
+    _check(resid32, "resid32", torch.float32, 2)
+    _check(weight32, "weight", torch.float32, 1)
+    H = resid32.shape[1]
+    if weight32.numel() != H:
+        raise KernelError(f"norm weight has {weight32.numel()} elements, width is {H}")
+    if delta is not None:
+        _check(delta, "delta", out_dtype, 2)
+        if delta.shape != resid32.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match the residual {tuple(resid32.shape)}")
+    rows = resid32.shape[0]
+    if row_idx is not None:
+        _check(row_idx, "row_idx", torch.int32, 1)
+        rows = row_idx.numel()
+    if out is None:
+        out = torch.empty((rows, H), dtype=out_dtype, device=resid32.device)
+    _check(out, "out", out_dtype, 2)
+    _ok(lib().acorn_add_rmsnorm(resid32.data_ptr(), _ptr(delta), weight32.data_ptr(), out.data_ptr(),
+                                _ptr(row_idx), rows, H, float(eps), dtype_code(out_dtype), _stream()),
+        "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _check(gate_up, "gate_up", None, 2)
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even width")
+    if out is None:
+        out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(out, "out", gate_up.dtype, 2)
+    _ok(lib().acorn_swiglu(gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, dtype_code(gate_up.dtype),
+                           _stream()), "swiglu")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _check(x, "x")
+    if x.dtype == dtype:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _ok(lib().acorn_cast(x.data_ptr(), out.data_ptr(), x.numel(), dtype_code(x.dtype), dtype_code(dtype),
+                         _stream()), "cast")
+    return out
+
+
+# ------------------------------------------------------------------ attention pieces
+
+
+def qk_rope_kv(qkv: torch.Tensor, q_weight32: torch.Tensor | None, k_weight32: torch.Tensor | None,
+               inv_freq: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+               block_table: torch.Tensor, page_base: torch.Tensor, k_pages: torch.Tensor | None,
+               v_pages: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
+               rotary_dim: int, interleaved: bool, eps: float, write_kv: bool = True) -> None:
+    """Per-head q/k norm, rotary encoding, K/V page write; q is updated in place inside ``qkv``."""
+    _check(qkv, "qkv", None, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {qkv.shape[1]} != (nq + 2 nkv) * d")
+    if head_dim > 1024 or rotary_dim > head_dim or rotary_dim % 2:
+        raise KernelError(f"head_dim {head_dim} / rotary_dim {rotary_dim} not supported (d <= 1024, even rotary_dim <= d)")
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    if inv_freq.numel() != rotary_dim // 2:
+        raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    for t, n in ((positions, "positions"), (token_row, "token_row"), (page_base, "page_base")):
+        _check(t, n, torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    for w, n in ((q_weight32, "q_norm weight"), (k_weight32, "k_norm weight")):
+        if w is not None:
+            _check(w, n, torch.float32, 1)
+            if w.numel() != head_dim:
+                raise KernelError(f"{n} must have head_dim entries")
+    P = 0
+    if write_kv:
+        _check(k_pages, "k_pages", qkv.dtype, 4)
+        _check(v_pages, "v_pages", qkv.dtype, 4)
+        if k_pages.shape[1] != num_kv_heads or k_pages.shape[3] != head_dim or v_pages.shape != k_pages.shape:
+            raise KernelError(f"cache pages {tuple(k_pages.shape)} do not fit nkv={num_kv_heads}, d={head_dim}")
+        P = k_pages.shape[2]
+    _ok(lib().acorn_qk_rope_kv(qkv.data_ptr(), _ptr(q_weight32), _ptr(k_weight32), inv_freq.data_ptr(),
+                               positions.data_ptr(), token_row.data_ptr(), block_table.data_ptr(),
+                               page_base.data_ptr(), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), T,
+                               num_heads, num_kv_heads, head_dim, rotary_dim, 1 if interleaved else 0,
+                               max(P, 1), float(eps), 1 if write_kv else 0, dtype_code(qkv.dtype), _stream()),
+        "qk_rope_kv")
+
+
+def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    block_table: torch.Tensor, page_base: torch.Tensor, token_row: torch.Tensor,
+                    positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                    scale: float, window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Paged causal attention for any mix of rows; ``q`` may be the head of a wider buffer
+    (row stride ``q_stride`` elements).  Returns [tokens, nq * d]."""
+    if head_dim > 512:
+        raise KernelError(f"plain attention supports head_dim <= 512, got {head_dim}")
+    if num_heads % num_kv_heads:
+        raise KernelError("num_heads must be a multiple of num_kv_heads")
+    _check(k_pages, "k_pages", q.dtype, 4)
+    _check(v_pages, "v_pages", q.dtype, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    if out is None:
+        out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(out, "out", q.dtype, 2)
+    _ok(lib().acorn_attention_plain(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(),
+                                    v_pages.data_ptr(), block_table.data_ptr(), page_base.data_ptr(),
+                                    block_table.stride(0), token_row.data_ptr(), positions.data_ptr(),
+                                    num_tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
+                                    float(scale), int(window or 0), dtype_code(q.dtype), _stream()),
+        "attention_plain")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [M, K] @ w [N, K]^T in true float32 (CUDA cores)."""
+    _check(w, "w", torch.float32, 2)
+    if a.dtype != torch.float32 or a.dim() != 2 or a.stride(1) != 1:
+        raise KernelError("a must be float32 [M, K] with contiguous K")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"inner sizes differ: a has K={K}, w has K={w.shape[1]}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _check(out, "out", torch.float32, 2)
+    _ok(lib().acorn_gemm_f32(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                             out.stride(0), M, N, K, _stream()), "gemm_f32")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x [T, K] times w [N, K] transposed.
+
+    float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
+    bfloat16 operands: the library matrix product (cuBLAS), float32 accumulation;
+    ``out_dtype=float32`` keeps the accumulator's precision (used for logits).
+    A weight stored in float32 under a bfloat16 engine is multiplied in float32.
+    """
+    out_dtype = out_dtype or x.dtype
+    if w.dtype == torch.float32:
+        y = gemm_f32(cast(x, torch.float32) if x.dtype != torch.float32 else x, w)
+        return y if out_dtype == torch.float32 else cast(y, out_dtype)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"linear: unsupported dtypes x={x.dtype}, w={w.dtype}")
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())
+
+
+# ------------------------------------------------------------------ sampling
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seed: torch.Tensor, counter: torch.Tensor, want_logprobs: bool = False):
+    """One token per row of float32 logits.  Per-row parameters are device tensors:
+    temperature/top_p float32, top_k int32, seed/counter int64 (used as unsigned)."""
+    _check(logits, "logits", torch.float32, 2)
+    R, V = logits.shape
+    _check(temperature, "temperature", torch.float32, 1)
+    _check(top_p, "top_p", torch.float32, 1)
+    _check(top_k, "top_k", torch.int32, 1)
+    _check(seed, "seed", torch.int64, 1)
+    _check(counter, "counter", torch.int64, 1)
+    for t in (temperature, top_k, top_p, seed, counter):
+        if t.numel() != R:
+            raise KernelError("per-row sampling parameters must have one entry per logits row")
+    tokens = torch.empty(R, dtype=torch.int32, device=logits.device)
+    logprobs = torch.empty(R, dtype=torch.float32, device=logits.device) if want_logprobs else None
+    _ok(lib().acorn_sample(logits.data_ptr(), logits.stride(0), R, V, temperature.data_ptr(), top_k.data_ptr(),
+                           top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(), tokens.data_ptr(),
+                           _ptr(logprobs), _stream()), "sample")
+    return tokens, logprobs
+
+
+def uniform(seed: int, counter: int) -> float:
+    """The uniform number the sampling kernel draws for (seed, counter), computed on the host."""
+    return float(lib_host().acorn_uniform(ctypes.c_uint64(seed & (2 ** 64 - 1)), ctypes.c_uint64(counter & (2 ** 64 - 1))))
+
+
+def lib_host():
+    """The library for its host-only helpers (no device needed)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    h = ctypes.CDLL(str(ensure_built()))
+    h.acorn_uniform.argtypes = _Sigs.acorn_uniform
+    h.acorn_uniform.restype = c_float
+    return h

@@ -1,0 +1,225 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A model is data: a :class:`ModelSpec` lists layers, each layer names its parts by
+*kind* (a registry key) with the sizes and constants as parameters, and a schedule
+says in which order layers run.  A part never learns which model it is in: it gets
+its parameters, a :class:`BuildContext` (dtype, device, page size, the shared
+position encodings) and, at run time, the step's :class:`StepInputs` and the cache
+handle of the schedule entry it runs for.
+
+Interfaces
+----------
+``Norm``              ``forward(x32) -> x``; ``add_forward(resid32, delta) -> x`` (updates resid32)
+``PositionEncoding``  constants for the mixers' kernels; ``apply(q, k, positions)`` for use alone
+``Mixer``             ``cache_needs()``; ``forward(x, inputs, cache) -> delta``
+``FeedForward``       ``forward(x, inputs) -> delta``
+``Block``             ``forward(resid32, delta, inputs, cache) -> (resid32, delta)``
+
+All activations are ``[tokens, width]`` over the flat token dimension of one step.
+The residual stream is kept in float32 (``resid32``); what a part adds to it
+(``delta``) is in the engine's activation dtype.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+
+# --------------------------------------------------------------------------- specs
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """One checkpoint tensor a part expects.
+
+    ``init`` tells the random-weights mode how to fill it: ``"matrix"`` N(0, sigma),
+    ``"norm"`` 1 + N(0, sigma_norm), ``"table"`` integers.
+    """
+
+    shape: tuple[int, ...]
+    init: str = "matrix"
+    optional: bool = False
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part by kind: the registry key, its sizes/constants, its weight-name prefix."""
+
+    kind: str
+    params: dict = field(default_factory=dict)
+    prefix: str = ""
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: the arrangement (``block``) and the parts it arranges."""
+
+    block: PartSpec
+    mixer: PartSpec
+    feed_forward: PartSpec
+    norms: dict[str, PartSpec]
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One run of a layer.  ``layer`` indexes ``ModelSpec.layers`` and may appear in
+    several entries.  ``reads_cache_of`` names an earlier entry whose cache this run
+    reads instead of writing one of its own."""
+
+    layer: int
+    reads_cache_of: int | None = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    vocab_size: int
+    hidden_size: int
+    embedding: str                      # tensor name of the token table [vocab, hidden]
+    layers: tuple[LayerSpec, ...]
+    schedule: tuple[ScheduleEntry, ...]
+    final_norm: PartSpec
+    head: str | None                    # tensor name of the output matrix; None: tied to embedding
+    positions: dict[str, PartSpec] = field(default_factory=dict)   # shared position encodings by name
+    head_optional_tie: bool = False     # head tensor may be absent: then it is the embedding
+
+
+@dataclass
+class BuildContext:
+    dtype: torch.dtype
+    device: torch.device
+    page_size: int
+    positions: dict[str, "PositionEncoding"] = field(default_factory=dict)
+
+
+# --------------------------------------------------------------------------- cache needs
+
+
+@dataclass(frozen=True)
+class KVNeeds:
+    """Keys and values in pages.  ``window`` None: every earlier key is read;
+    an integer w: a query at position p reads keys p-w+1 .. p."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+    @property
+    def group_key(self) -> tuple:
+        return ("kv", self.num_kv_heads, self.head_dim, self.window)
+
+
+@dataclass(frozen=True)
+class StateNeeds:
+    """Per-request state of fixed size, kept in float32 in a slot of the slot pool."""
+
+    shape: tuple[int, ...]
+
+
+@dataclass(frozen=True)
+class CacheNeeds:
+    kv: KVNeeds | None = None
+    state: StateNeeds | None = None
+
+
+# --------------------------------------------------------------------------- parts
+
+
+class Part:
+    """Base of all parts: declares checkpoint tensors and takes them when loaded."""
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        """Tensor names (relative to the part's prefix) -> spec."""
+        return {}
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Receives the loaded tensors (same relative names) on the device."""
+
+
+class Norm(Part):
+    def forward(self, x32: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, resid32: torch.Tensor, delta: torch.Tensor | None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        """resid32 += delta (in place, float32), then the norm of it."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds()
+
+    def forward(self, x: torch.Tensor, inputs: "Any", cache: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, inputs: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of a mixer, a feed-forward and norms around the residual stream."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: dict[str, Norm]):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = norms
+
+    def forward(self, resid32: torch.Tensor, delta: torch.Tensor | None, inputs: "Any",
+                cache: "Any") -> tuple[torch.Tensor, torch.Tensor]:
+        raise NotImplementedError
+
+
+# --------------------------------------------------------------------------- registries
+
+
+class Registry:
+    """Name -> factory.  An unknown name is an error that lists the known ones."""
+
+    def __init__(self, what: str):
+        self.what = what
+        self._items: dict[str, Callable] = {}
+
+    def register(self, name: str, factory: Callable | None = None):
+        if factory is None:
+            def deco(f):
+                self._items[name] = f
+                return f
+            return deco
+        self._items[name] = factory
+        return factory
+
+    def get(self, name: str) -> Callable:
+        try:
+            return self._items[name]
+        except KeyError:
+            raise KeyError(
+                f"unknown {self.what} '{name}'; known: {', '.join(sorted(self._items)) or '(none)'}"
+            ) from None
+
+    def names(self) -> list[str]:
+        return sorted(self._items)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._items
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block arrangement")
+
+
+def build_part(registry: Registry, spec: PartSpec, ctx: BuildContext, **extra):
+    """Instantiates ``spec.kind`` from ``registry`` with the spec's parameters."""
+    factory = registry.get(spec.kind)
+    return factory(ctx=ctx, **spec.params, **extra)
