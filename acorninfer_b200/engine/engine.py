@@ -1,0 +1,150 @@
+"""The engine: request life cycle and the step loop above the step function.
+
+``submit`` -> repeated ``step`` -> tokens.  A step asks the scheduler who runs, feeds all
+of it to the :class:`ModelRunner` as ONE batch (prompt portions beside decoded tokens),
+samples one token for every row that reached its last known token, records eos/length,
+and retires what finished.  Interface and meanings after the reference's ``Engine``
+(``acorninfer/engine/engine.py:133-378``): ``submit(prompt_ids, sampling, max_tokens=,
+eos_ids=) -> seq_id``, ``step() -> [TokenOutput]``, ``has_pending()``, ``drop(seq_id)``,
+``seqs[seq_id]``, ``assert_balanced()``.
+
+When pages run out: the scheduler preempts the oldest running request and recomputes it
+later (see scheduler).  A request that can never run because it alone needs more pages
+than the pool has (its prompt is checked at submit; its growth is not known then) is
+finished with ``stop_reason = "capacity"`` instead of waiting for ever.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+
+from ..config.engine_config import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .batch import StepEntry
+from .request import Request, RequestStatus
+from .runner import ModelRunner
+from .scheduler import Scheduler
+
+
+@dataclass
+class TokenOutput:
+    seq_id: int
+    token_id: int
+    finished: bool
+    stop_reason: str | None = None
+
+
+class Engine:
+    def __init__(self, runner: ModelRunner, *, max_running: int = 8, watermark_blocks: int = 8,
+                 chunked_budget: int | None = None, default_eos_ids=None):
+        self.runner = runner
+        self.manager = runner.manager
+        if any(watermark_blocks >= t for t in self.manager.total_pages()):
+            raise ValueError(f"watermark_blocks ({watermark_blocks}) must be < num_blocks ({self.manager.num_pages})")
+        self.scheduler = Scheduler(self.manager, max_running, watermark_blocks, chunked_budget,
+                                   runner.max_step_tokens)
+        self.sampler = Sampler(runner.device)
+        cfg_eos = getattr(runner.config, "eos_token_id", ())
+        self.default_eos_ids = frozenset(default_eos_ids if default_eos_ids is not None else cfg_eos)
+        self.seqs: dict[int, Request] = {}
+        self._next_id = 0
+        self.steps = 0
+
+    @classmethod
+    def from_config(cls, cfg: EngineConfig) -> "Engine":
+        runner = ModelRunner.from_model_dir(
+            cfg.model_dir, dtype=cfg.dtype, device=cfg.device, num_blocks=cfg.num_blocks, page_size=cfg.page_size,
+            max_requests=cfg.max_running, max_step_tokens=cfg.max_step_tokens)
+        return cls(runner, max_running=cfg.max_running, watermark_blocks=cfg.watermark_blocks,
+                   chunked_budget=cfg.chunked_budget)
+
+    # ------------------------------------------------------------------ requests
+
+    def submit(self, prompt_ids: list[int], sampling: SamplingParams | None = None, *, max_tokens: int,
+               eos_ids=None) -> int:
+        if not prompt_ids:
+            raise ValueError("prompt_ids must be non-empty")
+        if max_tokens < 1:
+            raise ValueError("max_tokens must be >= 1")
+        for t in prompt_ids:
+            if not (0 <= int(t) < self.runner.vocab_size):
+                raise ValueError(f"token id {t} outside the vocabulary (0..{self.runner.vocab_size - 1})")
+        need = self.manager.peak_pages(len(prompt_ids), self.scheduler.chunked_budget)
+        for n, total in zip(need, self.manager.total_pages()):
+            if n > total - self.scheduler.watermark:
+                raise ValueError(
+                    f"prompt needs {n} cache pages, the schedulable capacity is {total - self.scheduler.watermark} "
+                    f"({total} pages - watermark); it could never be admitted")
+        req = Request(self._next_id, [int(t) for t in prompt_ids], sampling or SamplingParams(temperature=0.0),
+                      max_tokens, frozenset(eos_ids) if eos_ids is not None else self.default_eos_ids)
+        self._next_id += 1
+        self.seqs[req.seq_id] = req
+        self.scheduler.add(req)
+        return req.seq_id
+
+    def drop(self, seq_id: int) -> None:
+        req = self.seqs.get(seq_id)
+        if req is not None and not req.is_finished:
+            raise ValueError(f"seq {seq_id} is still pending; cannot drop")
+        self.seqs.pop(seq_id, None)
+
+    def has_pending(self) -> bool:
+        return self.scheduler.has_pending()
+
+    def assert_balanced(self) -> None:
+        self.manager.assert_balanced()
+
+    # ------------------------------------------------------------------ the step
+
+    def step(self) -> list[TokenOutput]:
+        outputs: list[TokenOutput] = []
+        decision = self.scheduler.schedule()
+        if not decision.portions:
+            if self.scheduler.waiting and not self.scheduler.running:
+                req = self.scheduler.waiting[0]
+                need = self.manager.peak_pages(req.num_tokens, self.scheduler.chunked_budget)
+                if any(n > t - self.scheduler.watermark for n, t in zip(need, self.manager.total_pages())):
+                    # Not even an empty engine can hold it: it would wait for ever.
+                    self.scheduler.waiting.popleft()
+                    self._finish(req, "capacity")
+                    last = req.generated_ids[-1] if req.generated_ids else -1
+                    outputs.append(TokenOutput(req.seq_id, last, True, "capacity"))
+            return outputs
+        try:
+            entries, samplers = [], []
+            for p in decision.portions:
+                ids = p.request.all_ids[p.start:p.start + p.length]
+                entries.append(StepEntry(p.request.cache, ids, [p.length - 1] if p.samples else []))
+                if p.samples:
+                    samplers.append(p.request)
+            logits = self.runner.step(entries)
+            for p in decision.portions:
+                p.request.cursor = p.start + p.length
+            if samplers:
+                tokens, _ = self.sampler.sample(logits, [r.sampling for r in samplers],
+                                                [len(r.generated_ids) for r in samplers])
+                for req, tok in zip(samplers, tokens):
+                    self._record(req, tok, outputs)
+        finally:
+            for req in [r for r in self.scheduler.running if r.is_finished]:
+                self.scheduler.retire(req)
+        self.steps += 1
+        return outputs
+
+    def _finish(self, req: Request, reason: str) -> None:
+        req.stop_reason = reason
+        req.status = RequestStatus.FINISHED
+
+    def _record(self, req: Request, token_id: int, outputs: list[TokenOutput]) -> None:
+        req.generated_ids.append(token_id)
+        now = time.perf_counter()
+        if req.first_token_at is None:
+            req.first_token_at = now
+        req.last_token_at = now
+        if token_id in req.eos_ids:
+            self._finish(req, "stop")
+        elif len(req.generated_ids) >= req.max_tokens:
+            self._finish(req, "length")
+        outputs.append(TokenOutput(req.seq_id, token_id, req.is_finished, req.stop_reason))

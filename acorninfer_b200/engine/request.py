@@ -1,0 +1,51 @@
+"""A request inside the engine: its tokens, its sampling parameters, where it stands.
+
+Reference: ``Sequence`` / ``RequestStatus`` in ``acorninfer/engine/sequence.py:12-46``.
+``cursor`` counts the tokens of ``all_ids`` whose keys and values are in the cache; a
+request whose pages were taken away (preemption) starts again from cursor 0 over
+``all_ids`` (prompt plus what it has generated), which recomputes the same cache.
+"""
+
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+
+from ..sampling.params import SamplingParams
+
+
+class RequestStatus(enum.Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+@dataclass
+class Request:
+    seq_id: int
+    prompt_ids: list[int]
+    sampling: SamplingParams
+    max_tokens: int
+    eos_ids: frozenset[int]
+    generated_ids: list[int] = field(default_factory=list)
+    status: RequestStatus = RequestStatus.WAITING
+    stop_reason: str | None = None
+    cursor: int = 0                      # tokens of all_ids already in the cache
+    cache: object = None                 # RequestCache while running
+    preemptions: int = 0
+    created_at: float = field(default_factory=time.perf_counter)
+    first_token_at: float | None = None
+    last_token_at: float | None = None
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_ids) + len(self.generated_ids)
+
+    @property
+    def all_ids(self) -> list[int]:
+        return self.prompt_ids + self.generated_ids
+
+    @property
+    def is_finished(self) -> bool:
+        return self.status is RequestStatus.FINISHED

@@ -37,6 +37,7 @@ def unregister_architecture(name: str) -> None:
 
 
 def known_architectures() -> list[str]:
+    _ensure_builtin()
     return sorted(_ARCHITECTURES)
 
 

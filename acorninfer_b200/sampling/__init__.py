@@ -1,0 +1,1 @@
+from .params import SamplingParams  # noqa: F401

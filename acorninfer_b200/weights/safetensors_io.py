@@ -17,6 +17,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from dataclasses import dataclass
 from pathlib import Path
 
@@ -93,7 +94,9 @@ class SafetensorsFile:
         e = self.entries[name]
         if e.end == e.begin:
             return torch.empty(e.shape, dtype=e.dtype)
-        flat = torch.frombuffer(memoryview(self._map)[e.begin:e.end], dtype=e.dtype)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # the map is read-only; tensors are copied before use
+            flat = torch.frombuffer(memoryview(self._map)[e.begin:e.end], dtype=e.dtype)
         return flat.view(e.shape)
 
     def close(self) -> None:

@@ -1,0 +1,147 @@
+"""Generation through the entry point and the engine: greedy against the plain
+implementation, the first tokens of a sequence, long decoding, sampling with known uniforms,
+a token budget, and what happens when pages run out (preemption and recomputation give
+the same tokens; a request that can never fit is stopped)."""
+
+import pytest
+import torch
+
+from tests.plain import model as plain
+from tests.tiny import TINY_A, TINY_B, TINY_C, make_model_dir, random_tokens, read_weights, sizes_of
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, tiny in (("a", TINY_A), ("b", TINY_B), ("c", TINY_C)):
+        d = make_model_dir(tmp_path_factory.mktemp(name), tiny)
+        out[name] = (tiny, d, read_weights(d))
+    return out
+
+
+def follows_plain(sizes, weights, prompt, ids, slack):
+    """Every generated token is the plain model's best at its place, or within ``slack`` of it."""
+    logits = plain.forward(sizes, weights, ids[:-1])
+    for i in range(len(prompt), len(ids)):
+        row = logits[i - 1]
+        if float(row.max() - row[ids[i]]) > slack:
+            return False
+    return True
+
+
+@pytest.mark.parametrize("which", ["a", "b", "c"])
+def test_greedy_generate_matches_plain_float32(folders, which):
+    from acorninfer_b200 import generate
+    tiny, d, w = folders[which]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 10 + n) for n in (5, 9, 13, 1)]
+    got = generate(d, prompts, max_new_tokens=8, temperature=0.0, dtype="float32", page_size=tiny["page_size"],
+                   num_blocks=64, eos_ids=())
+    for p, ids in zip(prompts, got):
+        assert ids[:len(p)] == p and len(ids) == len(p) + 8
+        assert ids == plain.greedy_generate(sizes_of(cfg), w, p, 8) or follows_plain(sizes_of(cfg), w, p, ids, 1e-5)
+
+
+def test_greedy_generate_bfloat16_follows_plain_within_rounding(folders):
+    from acorninfer_b200 import generate
+    tiny, d, w = folders["b"]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 30 + n) for n in (7, 16, 23)]
+    got = generate(d, prompts, max_new_tokens=10, dtype="bfloat16", page_size=8, num_blocks=64, eos_ids=())
+    for p, ids in zip(prompts, got):
+        assert follows_plain(sizes_of(cfg), w, p, ids, 0.06)
+
+
+def test_first_tokens_and_eos(folders):
+    """A one-token prompt; and generation stops after an eos id, which is kept."""
+    from acorninfer_b200 import generate
+    tiny, d, w = folders["a"]
+    cfg = tiny["cfg"]
+    ref = plain.greedy_generate(sizes_of(cfg), w, [17], 6)
+    assert generate(d, [[17]], max_new_tokens=6, dtype="float32", page_size=4, num_blocks=16, eos_ids=())[0] == ref
+    eos = ref[3]
+    stopped = generate(d, [[17]], max_new_tokens=6, dtype="float32", page_size=4, num_blocks=16, eos_ids=(eos,))[0]
+    assert stopped == ref[:ref.index(eos, 1) + 1]
+
+
+def test_long_decoding_float32(folders):
+    """300 decoded tokens, crossing many pages, checked against the plain model's logits."""
+    from acorninfer_b200 import generate
+    tiny, d, w = folders["c"]
+    cfg = tiny["cfg"]
+    p = random_tokens(6, cfg.vocab_size, 4)
+    ids = generate(d, [p], max_new_tokens=300, dtype="float32", page_size=16, num_blocks=32, eos_ids=())[0]
+    assert len(ids) == 306 and follows_plain(sizes_of(cfg), w, p, ids, 1e-5)
+
+
+def test_temperature_sampling_uses_the_request_stream(folders):
+    from acorninfer_b200 import generate
+    from acorninfer_b200.kernels import ops
+    tiny, d, w = folders["b"]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 60 + n) for n in (1, 7, 16, 23)]
+    kw = dict(max_new_tokens=10, temperature=0.7, seed=5, dtype="float32", page_size=8, num_blocks=64, eos_ids=())
+    got = generate(d, prompts, chunked_budget=5, **kw)
+    assert got == generate(d, prompts, **kw)             # same tokens whatever the batching
+    alone = generate(d, prompts[2:3], **dict(kw, seed=7))[0]   # request 2 has seed 5 + 2
+    assert alone == got[2]
+    agree = total = 0
+    for i, (p, ids) in enumerate(zip(prompts, got)):
+        logits = plain.forward(sizes_of(cfg), w, ids[:-1])
+        for j in range(len(p), len(ids)):
+            u = ops.uniform(5 + i, j - len(p))
+            want, _, margin = plain.sample_with_uniform(plain.process_logits(logits[j - 1], 0.7), u)
+            if margin > 1e-4:
+                total += 1
+                agree += int(want == ids[j])
+    assert total >= 20 and agree == total
+
+
+def test_pages_run_out_preempts_and_recomputes_the_same_tokens(folders):
+    from acorninfer_b200.generate import build_engine, generate_with_engine
+    tiny, d, w = folders["a"]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 80 + n) for n in (12, 12, 9)]
+    roomy = build_engine(d, dtype="float32", page_size=4, num_blocks=64, watermark_blocks=0, max_running=3)
+    want = generate_with_engine(roomy, prompts, max_new_tokens=12, eos_ids=())
+    tight = build_engine(d, dtype="float32", page_size=4, num_blocks=9, watermark_blocks=0, max_running=3)
+    got = generate_with_engine(tight, prompts, max_new_tokens=12, eos_ids=())
+    assert got == want
+    tight.assert_balanced()
+
+
+def test_preemption_is_counted_and_capacity_stops_a_request_that_cannot_fit(folders):
+    from acorninfer_b200.generate import build_engine
+    from acorninfer_b200.sampling.params import SamplingParams
+    tiny, d, w = folders["a"]
+    eng = build_engine(d, dtype="float32", page_size=4, num_blocks=6, watermark_blocks=0, max_running=2)
+    a = eng.submit(list(range(1, 13)), SamplingParams(temperature=0.0), max_tokens=8, eos_ids=())
+    b = eng.submit(list(range(21, 33)), SamplingParams(temperature=0.0), max_tokens=3, eos_ids=())
+    while eng.has_pending():
+        eng.step()
+    assert eng.seqs[a].preemptions >= 1 and len(eng.seqs[a].generated_ids) == 8 and len(eng.seqs[b].generated_ids) == 3
+    ref = plain.greedy_generate(sizes_of(tiny["cfg"]), w, list(range(1, 13)), 8)
+    assert eng.seqs[a].all_ids == ref
+    # 4 + 40 tokens need 11 pages; the pool has 6: stopped with a reason, not waiting for ever
+    c = eng.submit([5, 6, 7, 8], SamplingParams(temperature=0.0), max_tokens=40, eos_ids=())
+    steps = 0
+    while eng.has_pending():
+        eng.step()
+        steps += 1
+        assert steps < 200
+    assert eng.seqs[c].stop_reason == "capacity" and 16 <= len(eng.seqs[c].generated_ids) < 40
+    eng.assert_balanced()
+    with pytest.raises(ValueError, match="never be admitted"):
+        eng.submit(list(range(1, 30)), max_tokens=1)
+
+
+def test_command_line(folders, capsys):
+    from acorninfer_b200.cli import main
+    tiny, d, w = folders["a"]
+    rc = main(["generate", "--model-dir", str(d), "--prompt-ids", "5,6,7", "--max-new-tokens", "4", "--dtype", "float32",
+               "--page-size", "4", "--num-blocks", "16"])
+    out = capsys.readouterr().out.strip().splitlines()[-1]
+    ids = [int(t) for t in out.split(",")]
+    assert rc == 0 and ids[:3] == [5, 6, 7] and 4 <= len(ids) <= 7

@@ -1,0 +1,114 @@
+"""The attention-side kernels alone: q/k norm + rotary + page write, and paged attention,
+against the plain formulas; inputs are made so that a far key, a window's edge or a page's
+edge decides the result."""
+
+import pytest
+import torch
+
+from tests.paged import gather_from_pages, rows_layout, scatter_to_pages
+from tests.plain import model as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from acorninfer_b200.kernels import ops as o
+    return o
+
+
+def rope_reference(x, positions, rot, theta, interleaved):
+    """x [T, heads, d] float64; rotates the first ``rot`` dims (plain formulas)."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    ang = (positions.to(torch.float32)[:, None] * inv[None]).double()
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+        out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, b * c + a * s
+    else:
+        a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+        out[..., :rot // 2], out[..., rot // 2:rot] = a * c - b * s, b * c + a * s
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,rot,inter,norm,P", [
+    (4, 2, 16, 16, False, True, 4), (10, 2, 48, 48, False, True, 16), (3, 3, 80, 32, True, True, 8),
+    (6, 1, 112, 112, False, False, 32), (2, 1, 272, 64, False, True, 16)])
+def test_qk_rope_kv(dtype, nq, nkv, d, rot, inter, norm, P):
+    theta, eps, NP = 5e5, 2e-6, 1400
+    lay = rows_layout([0, 37, 4095, 15], [21, 1, 2, 17], P, NP, seed=1)
+    T = lay["num_tokens"]
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dtype)
+    qw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    inv = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    k_pages = torch.zeros(NP, nkv, P, d, device=DEV, dtype=dtype)
+    v_pages = torch.zeros_like(k_pages)
+    src = qkv.double().cpu().view(T, nq + 2 * nkv, d)
+    ops().qk_rope_kv(qkv, qw, kw, inv, lay["positions"], lay["token_row"], lay["block_table"], lay["page_base"],
+                     k_pages, v_pages, nq, nkv, d, rot, inter, eps)
+    q, k, v = src[:, :nq], src[:, nq:nq + nkv], src[:, nq + nkv:]
+    if norm:
+        q = plain.rms_norm(q, qw.double().cpu(), eps)
+        k = plain.rms_norm(k, kw.double().cpu(), eps)
+    pos = lay["positions"].cpu()
+    q, k = rope_reference(q, pos, rot, theta, inter), rope_reference(k, pos, rot, theta, inter)
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    got_q = qkv.double().cpu().view(T, nq + 2 * nkv, d)[:, :nq]
+    assert torch.allclose(got_q, q, **tol)
+    at = 0
+    for r, (before, n) in enumerate(zip([0, 37, 4095, 15], [21, 1, 2, 17])):
+        for i in range(n):
+            p = before + i
+            page, slot = lay["tables"][r][p // P], p % P
+            assert torch.allclose(k_pages[page, :, slot].double().cpu(), k[at + i], **tol)
+            assert torch.equal(v_pages[page, :, slot].cpu(), qkv.cpu().view(T, -1, d)[at + i, nq + nkv:])
+        at += n
+    # pages of other rows and untouched slots stay zero
+    used = {(lay["tables"][r][(b + i) // P], (b + i) % P) for r, (b, n) in enumerate(zip([0, 37, 4095, 15], [21, 1, 2, 17])) for i in range(n)}
+    mask = torch.ones(NP, P, dtype=torch.bool)
+    for pg, sl in used:
+        mask[pg, sl] = False
+    assert float(k_pages.cpu().float().abs().sum(dim=(1, 3))[mask].sum()) == 0
+
+
+def dense_attention(q, k, v, scale, window, q_start):
+    """q [n, nq, d] at positions q_start..; k, v [L, nkv, d]: plain formulas on the tail."""
+    L = k.shape[0]
+    full_q = torch.zeros(L, q.shape[1], q.shape[2], dtype=q.dtype)
+    full_q[q_start:] = q
+    out = plain.causal_attention(full_q.transpose(0, 1), k.transpose(0, 1), v.transpose(0, 1), scale, window)
+    return out.transpose(0, 1)[q_start:]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,P,window", [(4, 2, 16, 4, None), (10, 2, 48, 16, None), (8, 1, 128, 16, None),
+                                               (6, 3, 80, 8, 13), (5, 5, 32, 32, 40)])
+def test_attention_plain(dtype, nq, nkv, d, P, window):
+    before, qlens = [0, 300, 129, 16, 0], [150, 1, 2, 1, 1]
+    lay = rows_layout(before, qlens, P, 200, seed=2)
+    scale = d ** -0.5
+    k_pages = torch.zeros(200, nkv, P, d, device=DEV, dtype=dtype)
+    v_pages = torch.zeros_like(k_pages)
+    qs, wants = [], []
+    for r, (b, n) in enumerate(zip(before, qlens)):
+        L = b + n
+        k = torch.randn(L, nkv, d).to(dtype)
+        v = torch.randn(L, nkv, d).to(dtype)
+        q = torch.randn(n, nq, d).to(dtype)
+        if r == 1:
+            # one far key stands out: key 7 matches the query, all others score low
+            k[7] = (q[0, :nkv] * 8).to(dtype)
+        scatter_to_pages(k_pages, lay["tables"][r], k.to(DEV), P)
+        scatter_to_pages(v_pages, lay["tables"][r], v.to(DEV), P)
+        qs.append(q)
+        wants.append(dense_attention(q.double(), k.double(), v.double(), scale, window, b))
+    q_all = torch.cat(qs).reshape(-1, nq * d).to(DEV)
+    wide = torch.cat([q_all, torch.randn(q_all.shape[0], 2 * nkv * d, device=DEV).to(dtype)], dim=1).contiguous()
+    out = ops().attention_plain(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                lay["token_row"], lay["positions"], lay["num_tokens"], nq, nkv, d, scale, window)
+    want = torch.cat(wants).reshape(-1, nq * d)
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(out.double().cpu(), want, **tol)

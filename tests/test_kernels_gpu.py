@@ -1,0 +1,86 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same operation, at
+sizes other than the engine tests use (widths that are no power of two, head sizes in steps
+of 16, odd head counts).  float32 inputs catch indexing faults (tolerance 1e-5); bfloat16
+inputs are compared at bfloat16's resolution."""
+
+import math
+
+import pytest
+import torch
+
+from tests.plain import model as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from acorninfer_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    table = torch.randn(331, 120, device=DEV).to(dtype)
+    ids = torch.randint(0, 331, (77,), device=DEV, dtype=torch.int32)
+    out = ops().embed(ids, table)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [48, 120, 1000, 4100])
+def test_add_rmsnorm(dtype, H):
+    rows, eps = 13, 3e-6
+    resid = torch.randn(rows, H, device=DEV)
+    delta = torch.randn(rows, H, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, device=DEV)
+    want_resid = resid + delta.float()
+    want = plain.rms_norm(want_resid.double(), w.double(), eps)
+    r = resid.clone()
+    out = ops().add_rmsnorm(r, delta, w, eps, dtype)
+    assert torch.allclose(r, want_resid, atol=1e-6)
+    assert torch.allclose(out.double(), want, **tol(dtype))
+    # norm only (no delta): the residual is untouched
+    r2 = resid.clone()
+    out2 = ops().add_rmsnorm(r2, None, w, eps, dtype)
+    assert torch.equal(r2, resid)
+    assert torch.allclose(out2.double(), plain.rms_norm(resid.double(), w.double(), eps), **tol(dtype))
+    # selected rows (one listed twice): normed into rows 0.., residual not written
+    idx = torch.tensor([5, 0, 5, 12], device=DEV, dtype=torch.int32)
+    r3 = resid.clone()
+    out3 = ops().add_rmsnorm(r3, delta, w, eps, dtype, row_idx=idx)
+    assert torch.equal(r3, resid)
+    assert torch.allclose(out3.double(), want[idx.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_and_cast(dtype):
+    gu = torch.randn(9, 2 * 200, device=DEV).to(dtype)
+    out = ops().swiglu(gu)
+    g, u = gu.double()[:, :200], gu.double()[:, 200:]
+    assert torch.allclose(out.double(), g * torch.sigmoid(g) * u, **tol(dtype))
+    x = torch.randn(1000, device=DEV)
+    assert torch.equal(ops().cast(x, torch.bfloat16), x.to(torch.bfloat16))
+    assert torch.equal(ops().cast(x.to(torch.bfloat16), torch.float32), x.to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (7, 331, 120), (130, 65, 33), (64, 64, 16), (3, 1000, 257)])
+def test_gemm_f32_is_true_float32(M, N, K):
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    out = ops().gemm_f32(a, w)
+    want = a.double() @ w.double().T
+    assert torch.allclose(out.double(), want, atol=1e-5 * math.sqrt(K), rtol=1e-5)
+    # a row's result does not depend on the other rows
+    assert torch.equal(ops().gemm_f32(a[:1].contiguous(), w)[0], out[0])
+
+
+def test_gemm_f32_shows_what_a_reduced_precision_mode_would_hide():
+    # 1 + 2^-12 is lost by a product that rounds its inputs to 10 mantissa bits (TF32) or to bfloat16
+    a = torch.full((4, 8), 1 + 2 ** -12, device=DEV)
+    w = torch.eye(8, device=DEV)
+    assert torch.equal(ops().gemm_f32(a, w), a)

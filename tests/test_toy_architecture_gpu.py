@@ -1,0 +1,152 @@
+"""Another architecture, defined here and nowhere in the framework: a mixer with state of its
+own (a running mean over the request's tokens, kept in a state slot), a windowed attention
+layer beside it, a layer that runs twice and a run that reads another run's cache.  It is
+registered, built from a model folder and stepped through the same runner and replay, cut in
+every way, and compared with a plain whole-sequence computation written here."""
+
+from dataclasses import dataclass
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+from acorninfer_b200.config.model_config import ModelConfig
+from acorninfer_b200.parts.base import (MIXERS, CacheNeeds, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry,
+                                        StateNeeds, TensorSpec)
+from acorninfer_b200.registry import register_architecture, unregister_architecture
+from tests import traces
+from tests.plain import model as plain
+from tests.tiny import random_tokens, read_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass(frozen=True)
+class ToyConfig(ModelConfig):
+    architecture: ClassVar[str] = "ToyStateForCausalLM"
+    hidden_size: int = 40
+    vocab_size: int = 97
+    num_heads: int = 6
+    num_kv_heads: int = 3
+    head_dim: int = 16
+    intermediate_size: int = 56
+    window: int = 9
+    eps: float = 1e-5
+    theta: float = 3e4
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+
+class RunningMean(Mixer):
+    """out[t] = W . mean(x[0..t]) over the tokens of the request so far.  The sum and the count
+    live in the request's state slot, so a portion continues where the last one stopped."""
+
+    def __init__(self, ctx, width):
+        self.ctx, self.width, self.w = ctx, width, None
+
+    def tensor_specs(self):
+        return {"mean_proj.weight": TensorSpec((self.width, self.width))}
+
+    def bind(self, tensors):
+        self.w = tensors["mean_proj.weight"].contiguous()
+
+    def cache_needs(self):
+        return CacheNeeds(state=StateNeeds((self.width + 1,)))
+
+    def forward(self, x, inputs, cache):
+        from acorninfer_b200.kernels import ops
+        out = torch.empty_like(x)
+        plan = inputs.plan
+        for r in range(plan.num_rows):
+            a, b = int(plan.row_start[r]), int(plan.row_start[r + 1])
+            st = cache.state[int(plan.row_slot[r])]
+            sums = st[:self.width] + torch.cumsum(x[a:b].float(), dim=0)
+            counts = st[self.width] + torch.arange(1, b - a + 1, device=x.device, dtype=torch.float32)
+            out[a:b] = (sums / counts[:, None]).to(x.dtype)
+            st[:self.width] = sums[-1]
+            st[self.width] = counts[-1]
+        return ops.linear(out, self.w, out_dtype=self.ctx.dtype)
+
+
+def toy_spec(cfg: ToyConfig) -> ModelSpec:
+    norm = {"width": cfg.hidden_size, "eps": cfg.eps}
+    ff = {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}
+
+    def attn(window):
+        return {"hidden_size": cfg.hidden_size, "num_heads": cfg.num_heads, "num_kv_heads": cfg.num_kv_heads,
+                "head_dim": cfg.head_dim, "qk_norm_eps": cfg.eps, "position": "rope", "scale": cfg.head_dim ** -0.5,
+                "window": window}
+
+    def layer(i, mixer):
+        p = f"model.layers.{i}."
+        return LayerSpec(PartSpec("prenorm", {}, p), mixer, PartSpec("swiglu", ff, p + "mlp."),
+                         {"mixer": PartSpec("rmsnorm", norm, p + "input_layernorm."),
+                          "feed_forward": PartSpec("rmsnorm", norm, p + "post_attention_layernorm.")})
+
+    layers = (layer(0, PartSpec("toy_running_mean", {"width": cfg.hidden_size}, "model.layers.0.mixer.")),
+              layer(1, PartSpec("attention", attn(cfg.window), "model.layers.1.self_attn.")),
+              layer(2, PartSpec("attention", attn(None), "model.layers.2.self_attn.")))
+    # layer 1 runs twice (each run keeps a cache of its own); the last run of layer 2 reads the
+    # cache its first run wrote
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, reads_cache_of=2))
+    return ModelSpec(cfg.vocab_size, cfg.hidden_size, "model.embed_tokens.weight", layers, schedule,
+                     PartSpec("rmsnorm", norm, "model.norm."), "lm_head.weight",
+                     {"rope": PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.theta})})
+
+
+def toy_plain(cfg: ToyConfig, weights, ids):
+    """Whole-sequence computation of the toy model in float64 from the plain formulas."""
+    w = {k: v.double() for k, v in weights.items()}
+    sizes = {"num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
+             "rms_norm_eps": cfg.eps, "rope_theta": cfg.theta}
+    ids = torch.as_tensor(ids)
+    pos = torch.arange(len(ids))
+    x = w["model.embed_tokens.weight"][ids]
+    kv_of_entry = {}
+    for entry, (layer, reads) in enumerate([(0, None), (1, None), (2, None), (1, None), (2, 2)]):
+        p = f"model.layers.{layer}."
+        h = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg.eps)
+        if layer == 0:
+            mean = torch.cumsum(h, 0) / torch.arange(1, len(ids) + 1, dtype=torch.float64)[:, None]
+            a = mean @ w[p + "mixer.mean_proj.weight"].T
+        else:
+            a, kv = plain.attention_block(h, w, p + "self_attn.", sizes, pos, cfg.window if layer == 1 else None,
+                                          kv_of_entry.get(reads))
+            kv_of_entry[entry] = kv
+        x = x + a
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg.eps), w, p + "mlp.")
+    return plain.rms_norm(x, w["model.norm.weight"], cfg.eps) @ w["lm_head.weight"].T
+
+
+@pytest.fixture(scope="module")
+def toy(tmp_path_factory):
+    from acorninfer_b200.weights.random_init import write_random_model
+    MIXERS.register("toy_running_mean", RunningMean)
+    register_architecture(ToyConfig.architecture, ToyConfig, toy_spec)
+    cfg = ToyConfig()
+    d = write_random_model(tmp_path_factory.mktemp("toy"), cfg, seed=9, sigma=0.08, sigma_norm=0.1)
+    yield cfg, d
+    unregister_architecture(ToyConfig.architecture)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 8e-2)])
+def test_toy_architecture_runs_through_the_same_runner_and_replay(toy, dtype, tol):
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.replay import TraceSession
+
+    cfg, d = toy
+    w = read_weights(d)
+    reqs = {f"t{i}": random_tokens(n, cfg.vocab_size, 70 + i) for i, n in enumerate([45, 38, 61, 50, 33])}
+    ref = {rid: toy_plain(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    for cut in ("whole", "decode_tail", "portions", "mixed"):
+        steps = getattr(traces, cut)(reqs)
+        runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=-(-traces.max_live_tokens(steps) // 8),
+                                            page_size=8, max_requests=4)
+        assert len(runner.manager.groups) == 2 and len(runner.manager.state) == 1   # window, full; one state
+        got = traces.collect(TraceSession(runner).step, steps)
+        runner.manager.assert_balanced()
+        for (rid, pos), row in got.items():
+            assert np.abs(row - ref[rid][pos]).max() < tol, (cut, rid, pos)
