@@ -19,7 +19,7 @@ __all__ = ["EngineConfig", "ConfigError", "ModelConfig", "Qwen3Config", "Samplin
 def __getattr__(name):
     # Engine parts import torch and the kernels; load them on first use.
     if name == "generate":
-        from .generate import generate
+        from .generation import generate
         return generate
     if name == "Engine":
         from .engine.engine import Engine

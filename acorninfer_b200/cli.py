@@ -55,7 +55,7 @@ def main(argv=None) -> int:
         print(write_random_model(args.out, cfg, args.seed, args.sigma, args.sigma_norm))
         return 0
 
-    from .generate import build_engine, generate_with_engine
+    from .generation import build_engine, generate_with_engine
 
     if (args.prompt is None) == (args.prompt_ids is None):
         parser.error("give exactly one of --prompt and --prompt-ids")

@@ -100,7 +100,7 @@ def test_temperature_sampling_uses_the_request_stream(folders):
 
 
 def test_pages_run_out_preempts_and_recomputes_the_same_tokens(folders):
-    from acorninfer_b200.generate import build_engine, generate_with_engine
+    from acorninfer_b200.generation import build_engine, generate_with_engine
     tiny, d, w = folders["a"]
     cfg = tiny["cfg"]
     prompts = [random_tokens(n, cfg.vocab_size, 80 + n) for n in (12, 12, 9)]
@@ -113,7 +113,7 @@ def test_pages_run_out_preempts_and_recomputes_the_same_tokens(folders):
 
 
 def test_preemption_is_counted_and_capacity_stops_a_request_that_cannot_fit(folders):
-    from acorninfer_b200.generate import build_engine
+    from acorninfer_b200.generation import build_engine
     from acorninfer_b200.sampling.params import SamplingParams
     tiny, d, w = folders["a"]
     eng = build_engine(d, dtype="float32", page_size=4, num_blocks=6, watermark_blocks=0, max_running=2)
