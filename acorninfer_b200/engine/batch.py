@@ -58,10 +58,14 @@ class StepPlan:
     row_lens: list[int]
     max_q_len: int
     all_decode: bool            # every row is a single token
+    q_tiles: np.ndarray = None  # [n_tiles, 2]: (row, first token within the row) of each 64-token query tile
 
     @property
     def num_logits(self) -> int:
         return int(self.logit_tokens.size)
+
+
+Q_TILE = 64     # query tokens per tile of the prefill attention kernel
 
 
 def _table_stride(pages: int) -> int:
@@ -137,8 +141,10 @@ def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
             kv_len[r] = new_len
             base[r] = e.cache.page_base[g.index]
         groups.append(GroupPlan(kv_len, base, bt, int(kv_len.max()) if R else 0))
+    tiles = [(r, q0) for r, n in enumerate(lens) for q0 in range(0, n, Q_TILE)]
     return StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
-                    np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens))
+                    np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens),
+                    np.asarray(tiles, np.int32).reshape(-1, 2))
 
 
 # --------------------------------------------------------------------------- device side
@@ -167,6 +173,7 @@ class StepInputs:
     logit_tokens: object
     groups: list[GroupInputs]
     plan: StepPlan
+    q_tiles: object = None
     scratch: dict = field(default_factory=dict)     # per-step products shared by parts (e.g. split plans)
 
     @property
@@ -211,6 +218,7 @@ class StepWorkspace:
         put("row_pos", R)
         put("row_slot", R)
         put("logit_tokens", plan.num_logits)
+        put("q_tiles", plan.q_tiles.size)
         for i, g in enumerate(plan.groups):
             put(f"g{i}.kv_len", R)
             put(f"g{i}.page_base", R)
@@ -230,7 +238,7 @@ class StepWorkspace:
         arrays = {
             "token_ids": plan.token_ids, "positions": plan.positions, "token_row": plan.token_row,
             "row_start": plan.row_start, "row_pos": plan.row_pos, "row_slot": plan.row_slot,
-            "logit_tokens": plan.logit_tokens,
+            "logit_tokens": plan.logit_tokens, "q_tiles": plan.q_tiles.reshape(-1),
         }
         for gi, g in enumerate(plan.groups):
             arrays[f"g{gi}.kv_len"] = g.kv_len
@@ -253,4 +261,5 @@ class StepWorkspace:
             bt = view(f"g{gi}.block_table").view(plan.num_rows, g.block_table.shape[1])
             groups.append(GroupInputs(view(f"g{gi}.kv_len"), view(f"g{gi}.page_base"), bt, g.max_kv_len))
         return StepInputs(plan.num_tokens, plan.num_rows, view("token_ids"), view("positions"), view("token_row"),
-                          view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan)
+                          view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan,
+                          view("q_tiles").view(-1, 2))

@@ -90,6 +90,16 @@ class Engine:
             raise ValueError(f"seq {seq_id} is still pending; cannot drop")
         self.seqs.pop(seq_id, None)
 
+    def abort(self, seq_id: int) -> None:
+        """Ends a pending request now (``stop_reason = "abort"``); what it holds goes back."""
+        req = self.seqs.get(seq_id)
+        if req is None or req.is_finished:
+            return
+        if req in self.scheduler.waiting:
+            self.scheduler.waiting.remove(req)
+        self._finish(req, "abort")
+        self.scheduler.retire(req)
+
     def has_pending(self) -> bool:
         return self.scheduler.has_pending()
 

@@ -112,6 +112,7 @@ class ModelRunner:
         validate_entries(entries, self.vocab_size, self.max_step_tokens)
         self.reserve(entries)
         plan = plan_step(entries, self.manager)
+        self.last_plan = plan
         inputs = self.workspace.upload(plan)
         logits = self.decoder.forward(inputs, self.caches)
         for e in entries:

@@ -53,6 +53,14 @@ class _Sigs:
     acorn_attention_plain = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                              c_void_p]
+    acorn_attention_decode = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                              c_int, c_void_p, c_void_p, c_void_p]
+    acorn_attention_decode_supported = [c_int, c_int, c_int]
+    acorn_attention_prefill = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                               c_void_p]
+    acorn_attention_prefill_supported = [c_int, c_int, c_int]
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
     acorn_sample = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_void_p, c_void_p]
@@ -82,8 +90,13 @@ def _check(t: torch.Tensor, name: str, dtype=None, dims: int | None = None) -> N
         raise KernelError(f"{name} must have {dims} dimensions, got shape {tuple(t.shape)}")
 
 
+LAUNCHES = 0      # kernels of this library launched so far (for reports)
+
+
 def _ok(code: int, what: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code == 10001:
         raise KernelError(f"{what}: sizes or dtypes not supported by this kernel")
@@ -227,6 +240,76 @@ def attention_plain(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pag
                                     num_tokens, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
                                     float(scale), int(window or 0), dtype_code(q.dtype), _stream()),
         "attention_plain")
+    return out
+
+
+def attention_decode_supported(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return bool(lib().acorn_attention_decode_supported(num_heads, num_kv_heads, head_dim))
+
+
+def attention_prefill_supported(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return bool(lib().acorn_attention_prefill_supported(num_heads, num_kv_heads, head_dim))
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, page_base: torch.Tensor, token_row: torch.Tensor,
+                     positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                     scale: float, window: int | None, num_splits: int, token_list: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None, scratch: tuple | None = None) -> torch.Tensor:
+    """Split-K decode attention (bfloat16) for single-token rows: the tokens 0..num_tokens-1, or
+    those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
+    not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
+    part_lse float32 [n, nq, splits]) is made here when absent and num_splits > 1."""
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode takes bfloat16")
+    if not attention_decode_supported(num_heads, num_kv_heads, head_dim):
+        raise KernelError(f"attention_decode does not take nq={num_heads}, nkv={num_kv_heads}, d={head_dim}")
+    _check(k_pages, "k_pages", q.dtype, 4)
+    _check(v_pages, "v_pages", q.dtype, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    n = num_tokens if token_list is None else token_list.numel()
+    if n > 65535 or not (1 <= num_splits <= 65535):
+        raise KernelError(f"attention_decode: {n} tokens / {num_splits} splits beyond the grid limits")
+    if out is None:
+        out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    part_o = part_lse = None
+    if num_splits > 1:
+        if scratch is None:
+            scratch = (torch.empty((n, num_heads, num_splits, head_dim), dtype=torch.float32, device=q.device),
+                       torch.empty((n, num_heads, num_splits), dtype=torch.float32, device=q.device))
+        part_o, part_lse = scratch
+        if part_o.numel() < n * num_heads * num_splits * head_dim or part_lse.numel() < n * num_heads * num_splits:
+            raise KernelError("attention_decode: scratch too small")
+    _ok(lib().acorn_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                                     block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
+                                     token_row.data_ptr(), positions.data_ptr(), _ptr(token_list), n, num_heads,
+                                     num_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window or 0),
+                                     num_splits, _ptr(part_o), _ptr(part_lse), _stream()), "attention_decode")
+    return out
+
+
+def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, page_base: torch.Tensor, row_start: torch.Tensor,
+                      row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
+                      num_kv_heads: int, head_dim: int, scale: float, window: int | None,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core prefill attention (bfloat16) for the query tiles listed in ``tiles``
+    (int32 [n, 2]: row, first token within the row; 64 tokens a tile at most)."""
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill takes bfloat16")
+    if not attention_prefill_supported(num_heads, num_kv_heads, head_dim):
+        raise KernelError(f"attention_prefill does not take nq={num_heads}, nkv={num_kv_heads}, d={head_dim}")
+    _check(k_pages, "k_pages", q.dtype, 4)
+    _check(v_pages, "v_pages", q.dtype, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(tiles, "tiles", torch.int32, 2)
+    if out is None:
+        out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _ok(lib().acorn_attention_prefill(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                                      block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
+                                      row_start.data_ptr(), row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0],
+                                      num_heads, num_kv_heads, head_dim, k_pages.shape[2], float(scale),
+                                      int(window or 0), _stream()), "attention_prefill")
     return out
 
 

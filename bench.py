@@ -1,0 +1,299 @@
+"""Benchmark of acorninfer_b200: decode tokens/s at Qwen3-8B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers N] [--impl ours|reference]
+
+Prints ONE JSON line.  A step is one decode step of a batch of 8 requests at the context
+length of the reference configuration (2,048-token prompts + 2,048 generated tokens: the
+timed steps end at context 4,096).  ``value`` is decoded tokens per second timed on the
+device with CUDA events (token ids prepared beforehand, sampling kernel included);
+``e2e`` is the same through ``Engine.step()``: host token ids in, sampled ids out, every
+step.  ``prefill`` is one 2,048-token prompt in one step; ``points`` are decode at batch
+1 and 64; ``roofline`` compares the bytes a decode step must read (every weight once,
+the cache of the live requests) with the measured copy bandwidth.  Weights are random
+(seeded N(0, 0.02), norms 1), token ids uniform random: synthetic data.  Weights
+(15 GB) are far larger than L2, so no L2 flush is needed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=151936,
+                tie_word_embeddings=False, bos_token_id=None, eos_token_id=())
+CONTEXT = 4096
+PROMPT = 2048
+PAGE = 16
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_numbers(c: dict, layers: int) -> dict:
+    H, nq, nkv, d, I, V = (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
+                           c["intermediate_size"], c["vocab_size"])
+    per_layer = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I
+    return {"layer_params": per_layer, "weight_bytes": 2 * (layers * per_layer + V * H),
+            "kv_bytes_per_token": 2 * layers * 2 * nkv * d, "nq": nq, "d": d, "H": H, "V": V}
+
+
+def prefill_flops(nums: dict, layers: int, T: int) -> float:
+    gemm = 2.0 * T * layers * nums["layer_params"] + 2.0 * nums["V"] * nums["H"]
+    attn = layers * nums["nq"] * nums["d"] * 4.0 * (T * (T + 1) / 2)
+    return gemm + attn
+
+
+def synthetic_requests(runner, B: int, length: int, tag: str):
+    """B live requests that hold ``length`` tokens each: pages taken through the manager, their
+    contents random (what a prefill of random weights and tokens would leave, in distribution)."""
+    out = []
+    for i in range(B):
+        rc = runner.open(f"{tag}{i}")
+        runner.manager.extend(rc, length)
+        runner.manager.commit(rc, length)
+        out.append(rc)
+    return out
+
+
+def time_decode(runner, sampler, B: int, steps: int, warmup: int, ctx_end: int, torch):
+    """Device-timed decode at batch B ending at context ``ctx_end``: tokens prepared beforehand,
+    one step function call and one sampling launch per step, no host read in the loop."""
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.kernels import ops
+    from acorninfer_b200.sampling.params import SamplingParams
+
+    reqs = synthetic_requests(runner, B, ctx_end - steps - warmup, f"b{B}_")
+    g = torch.Generator().manual_seed(B)
+    toks = torch.randint(0, runner.vocab_size, (steps + warmup, B), generator=g).tolist()
+    greedy = [SamplingParams(temperature=0.0)] * B
+    dev = runner.device
+    t_par = torch.zeros(B, dtype=torch.float32, device=dev)
+    k_par = torch.zeros(B, dtype=torch.int32, device=dev)
+    p_par = torch.ones(B, dtype=torch.float32, device=dev)
+    s_par = torch.zeros(B, dtype=torch.int64, device=dev)
+
+    def one(i):
+        logits = runner.step([StepEntry(rc, [toks[i][r]], [0]) for r, rc in enumerate(reqs)])
+        return ops.sample(logits, t_par, k_par, p_par, s_par, s_par)[0]
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches0 = ops.LAUNCHES + getattr(runner, "graph_kernel_launches", 0)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        last = one(i)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    launches = ops.LAUNCHES + getattr(runner, "graph_kernel_launches", 0) - launches0
+    assert int(last.min()) >= 0
+    mean_ctx = ctx_end - steps / 2
+    for rc in reqs:
+        runner.close(rc)
+    return {"ms_per_step": ms / steps, "tok_s": B * steps / (ms / 1e3), "launches": launches, "mean_context": mean_ctx}
+
+
+def time_prefill(runner, T: int, repeats: int, torch):
+    from acorninfer_b200.engine.batch import StepEntry
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, runner.vocab_size, (T,), generator=g).tolist()
+    best = None
+    for i in range(repeats + 1):
+        rc = runner.open(f"p{i}")
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(rc, toks, [T - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        runner.close(rc)
+        if i > 0:
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def time_e2e(runner, B: int, steps: int, warmup: int, ctx_end: int, torch):
+    """The same metric through the public engine: ``Engine.submit`` then ``Engine.step()``;
+    every step copies that step's token ids and tables from pinned host memory to the device and
+    reads the sampled token ids back."""
+    from acorninfer_b200.engine.engine import Engine
+    from acorninfer_b200.sampling.params import SamplingParams
+
+    engine = Engine(runner, max_running=B, watermark_blocks=0, chunked_budget=2048, default_eos_ids=())
+    # Prompts go through the engine in portions of 2,048 tokens; requests that finish their prompt
+    # early decode while the others are still being read, so the prompts are shortened by the
+    # number of such steps and the timed steps end at the context length.
+    prefill_steps = -(-B * ctx_end // 2048)
+    prompt_len = ctx_end - steps - warmup - prefill_steps
+    g = torch.Generator().manual_seed(100 + B)
+    prompts = torch.randint(0, runner.vocab_size, (B, prompt_len), generator=g).tolist()
+    for p in prompts:
+        engine.submit(p, SamplingParams(temperature=0.0), max_tokens=ctx_end, eos_ids=())
+    while any(not r.generated_ids for r in engine.seqs.values()):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    n = steps
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    produced = 0
+    for _ in range(n):
+        produced += len(engine.step())
+    end.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = max(start.elapsed_time(end), wall * 1e3)
+    context_now = max(r.num_tokens for r in engine.seqs.values())
+    lay_ints = 3 * B + (B + 1) + 2 * B + B + sum(2 * B + B * g.block_table.shape[1]
+                                                   for g in runner.last_plan.groups) if hasattr(runner, "last_plan") else 0
+    for sid in list(engine.seqs):
+        engine.abort(sid)
+        engine.drop(sid)
+    engine.assert_balanced()
+    return {"value": produced / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms / n, "steps": n,
+            "context_end": context_now,
+            "h2d_bytes_per_step": 4 * lay_ints + 8 * 5 * B + 16 * B, "d2h_bytes_per_step": 4 * B}
+
+
+def reference_arm(args) -> int:
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "acorninfer").is_dir():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this box"}))
+        return 0
+    print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired yet"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                    help="fewer layers than the configuration has (sizes of a layer stay)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="only the batch of the headline value")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from acorninfer_b200.config.model_config import Qwen3Config
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.kernels import ops
+
+    pk = peaks()
+    conf = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    cfg = Qwen3Config(**conf)
+    nums = model_numbers(conf, args.layers)
+    max_b = max(args.batch, 1 if args.skip_points else 64)
+    num_blocks = max_b * CONTEXT // PAGE + 2 * (PROMPT // PAGE) + 64
+    runner = ModelRunner.from_random(cfg, seed=0, sigma=0.02, dtype="bfloat16", num_blocks=num_blocks, page_size=PAGE,
+                                     max_requests=max_b + 2, max_step_tokens=4096)
+    for g in runner.manager.groups:
+        g.storage.normal_(0, 1)
+    sampler = None
+
+    clocks = ClockSampler()
+    clocks.start()
+    head = time_decode(runner, sampler, args.batch, args.steps, args.warmup, CONTEXT, torch)
+    clock_info = clocks.stop()
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(time_decode(runner, sampler, b, args.steps, args.warmup, CONTEXT, torch)["tok_s"], 1)
+    pre_ms = time_prefill(runner, PROMPT, 3, torch)
+    e2e = time_e2e(runner, args.batch, args.steps, args.warmup, CONTEXT, torch)
+
+    step_bytes = nums["weight_bytes"] + args.batch * head["mean_context"] * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
+    flops = prefill_flops(nums, args.layers, PROMPT)
+    line = {
+        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-8B layer sizes, 1 B200)",
+        "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(head["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "Qwen3-8B sizes, random weights", "layers": args.layers,
+                   "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": 4096, "q_heads": 32, "kv_heads": 8,
+                   "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"]},
+        "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": head["launches"],
+        "prefill": {"value": round(PROMPT / (pre_ms / 1e3), 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_info,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

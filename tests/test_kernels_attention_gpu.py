@@ -112,3 +112,93 @@ def test_attention_plain(dtype, nq, nkv, d, P, window):
     want = torch.cat(wants).reshape(-1, nq * d)
     tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
     assert torch.allclose(out.double().cpu(), want, **tol)
+
+
+def build_case(before, qlens, nq, nkv, d, P, window, num_pages, seed, standout_row=None):
+    """Random paged K/V and queries for rows with ``before`` cached tokens and ``qlens`` new ones;
+    returns the device inputs and the plain float64 result [tokens, nq * d]."""
+    dtype = torch.bfloat16
+    num_pages = max(num_pages, sum(-(-(b + n) // P) for b, n in zip(before, qlens)) + 7)
+    lay = rows_layout(before, qlens, P, num_pages, seed=seed)
+    torch.manual_seed(seed)
+    k_pages = torch.zeros(num_pages, nkv, P, d, device=DEV, dtype=dtype)
+    v_pages = torch.zeros_like(k_pages)
+    qs, wants = [], []
+    for r, (b, n) in enumerate(zip(before, qlens)):
+        L = b + n
+        k, v, q = torch.randn(L, nkv, d).to(dtype), torch.randn(L, nkv, d).to(dtype), torch.randn(n, nq, d).to(dtype)
+        if r == standout_row and L > 70:
+            # a far key decides: key 3 is aligned with the last query of the row, its value is large
+            k[3] = (q[-1].view(nkv, nq // nkv, d)[:, 0] * 6).to(dtype)
+            v[3] = 5.0
+        scatter_to_pages(k_pages, lay["tables"][r], k.to(DEV), P)
+        scatter_to_pages(v_pages, lay["tables"][r], v.to(DEV), P)
+        qs.append(q)
+        wants.append(dense_attention(q.double(), k.double(), v.double(), d ** -0.5, window, b))
+    q_all = torch.cat(qs).reshape(-1, nq * d).to(DEV)
+    wide = torch.cat([q_all, torch.randn(q_all.shape[0], 2 * nkv * d, device=DEV).to(dtype)], dim=1).contiguous()
+    row_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    row_pos = torch.tensor(before, dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) for q0 in range(0, n, 64)], dtype=torch.int32,
+                         device=DEV).view(-1, 2)
+    return lay, wide, k_pages, v_pages, row_start, row_pos, tiles, torch.cat(wants).reshape(-1, nq * d)
+
+
+BF16_TOL = dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,d,P,window", [(32, 8, 128, 16, None), (4, 2, 16, 4, None), (8, 1, 32, 8, None),
+                                               (10, 2, 48, 16, None), (6, 3, 80, 8, 50), (16, 1, 64, 32, None),
+                                               (5, 5, 112, 16, 129), (4, 2, 256, 16, None)])
+@pytest.mark.parametrize("splits", [1, 3, 16])
+def test_attention_decode_kernel(nq, nkv, d, P, window, splits):
+    before = [0, 1, 63, 64, 65, 700, 127, 2000]           # one key; page and chunk edges; long rows
+    qlens = [1] * len(before)
+    lay, wide, k_pages, v_pages, _, _, _, want = build_case(before, qlens, nq, nkv, d, P, window, 400, 3, standout_row=5)
+    out = ops().attention_decode(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                 lay["token_row"], lay["positions"], len(before), nq, nkv, d, d ** -0.5, window, splits)
+    assert torch.allclose(out.double().cpu(), want, **BF16_TOL)
+    # the plain kernel agrees too, and a second run gives the same bits
+    again = ops().attention_decode(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                   lay["token_row"], lay["positions"], len(before), nq, nkv, d, d ** -0.5, window, splits)
+    assert torch.equal(out, again)
+
+
+def test_attention_decode_token_list_leaves_other_rows():
+    nq, nkv, d, P = 8, 2, 64, 16
+    before, qlens = [10, 300, 77, 5], [1, 1, 1, 1]
+    lay, wide, k_pages, v_pages, _, _, _, want = build_case(before, qlens, nq, nkv, d, P, None, 100, 4)
+    out = torch.full((4, nq * d), 7.0, device=DEV, dtype=torch.bfloat16)
+    chosen = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    ops().attention_decode(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                           lay["token_row"], lay["positions"], 4, nq, nkv, d, d ** -0.5, None, 4, token_list=chosen,
+                           out=out)
+    assert torch.allclose(out[[1, 3]].double().cpu(), want[[1, 3]], **BF16_TOL)
+    assert bool((out[[0, 2]] == 7.0).all())
+
+
+def test_attention_decode_refuses_what_it_cannot_compute():
+    from acorninfer_b200.kernels.ops import KernelError
+    assert not ops().attention_decode_supported(34, 2, 64)       # 17 query heads a group
+    assert not ops().attention_decode_supported(8, 2, 72)        # head size not a multiple of 16
+    with pytest.raises(KernelError):
+        x = torch.zeros(1, 8 * 72 * 2, device=DEV, dtype=torch.bfloat16)
+        pages = torch.zeros(2, 2, 16, 72, device=DEV, dtype=torch.bfloat16)
+        i32 = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops().attention_decode(x, x.stride(0), pages, pages, i32.view(1, 1), i32, i32, i32, 1, 8, 2, 72, 1.0, None, 1)
+
+
+@pytest.mark.parametrize("nq,nkv,d,P,window", [(32, 8, 128, 16, None), (4, 2, 16, 4, None), (8, 1, 32, 8, None),
+                                               (10, 2, 48, 16, None), (6, 3, 80, 8, 50), (5, 5, 112, 32, 129)])
+def test_attention_prefill_kernel(nq, nkv, d, P, window):
+    # portions that start inside a request, tiles that end inside a page, single tokens beside them
+    before = [0, 130, 64, 500, 0, 31]
+    qlens = [150, 64, 1, 2, 1, 65]
+    lay, wide, k_pages, v_pages, row_start, row_pos, tiles, want = build_case(before, qlens, nq, nkv, d, P, window, 400, 5,
+                                                                             standout_row=3)
+    out = ops().attention_prefill(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                  row_start, row_pos, tiles, sum(qlens), nq, nkv, d, d ** -0.5, window)
+    assert torch.allclose(out.double().cpu(), want, **BF16_TOL)
+    plain_out = ops().attention_plain(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                      lay["token_row"], lay["positions"], sum(qlens), nq, nkv, d, d ** -0.5, window)
+    assert torch.allclose(out.float(), plain_out.float(), **BF16_TOL)
