@@ -59,8 +59,8 @@ class CacheManager:
                  page_size: int, num_slots: int, dtype=None, device=None, allocate: bool = True):
         """``kv_needs`` / ``state_needs`` map schedule-entry index -> what that entry's mixer
         keeps.  ``num_pages`` is the size of every group's pool."""
-        if page_size < 1:
-            raise ValueError(f"page_size must be >= 1, got {page_size}")
+        if page_size < 1 or page_size & (page_size - 1):
+            raise ValueError(f"page_size must be a power of two, got {page_size}")
         self.page_size = page_size
         self.num_pages = num_pages
         self.groups: list[CacheGroup] = []

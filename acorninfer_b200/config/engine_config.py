@@ -35,8 +35,8 @@ class EngineConfig:
         object.__setattr__(self, "dtype", DTYPE_NAMES[self.dtype])
         if self.num_blocks < 1:
             raise ValueError(f"num_blocks must be >= 1, got {self.num_blocks}")
-        if self.page_size < 1 or self.page_size > 256:
-            raise ValueError(f"page_size must be in 1..256, got {self.page_size}")
+        if self.page_size < 1 or self.page_size > 256 or self.page_size & (self.page_size - 1):
+            raise ValueError(f"page_size must be a power of two in 1..256, got {self.page_size}")
         if self.max_running < 1:
             raise ValueError(f"max_running must be >= 1, got {self.max_running}")
         if self.watermark_blocks < 0:

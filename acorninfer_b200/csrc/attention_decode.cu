@@ -2,8 +2,8 @@
 // (token, kv head, split), all query heads of the kv head's group share every K/V tile.
 //
 // For the token at position p of its request the CTA reads keys lo..p
-// (lo = window ? max(0, p - window + 1) : 0) of its split, 64 keys a chunk, double-buffered
-// with cp.async through the block table.  The group's query heads (rep = nq / nkv <= 16) are
+// (lo = window ? max(0, p - window + 1) : 0) of its split, 64 keys a chunk, in a three-stage
+// cp.async pipeline through the block table.  The group's query heads (rep = nq / nkv <= 16) are
 // the 16 rows of an m16n8k16 tensor-core tile: S = Q K^T, online softmax in float32 (base 2),
 // O += P V.  Each of the 4 warps takes 16 keys of a chunk and keeps its own running
 // (max, sum, O); the warps are merged through shared memory at the end.  With one split the
@@ -17,6 +17,9 @@
 
 #define DEC_THREADS 128
 #define DEC_CHUNK 64
+#ifndef DEC_STAGES
+#define DEC_STAGES 3
+#endif
 
 struct DecodeParams {
     const bf16* q;            // [tokens, q_stride]: query heads first in each row
@@ -31,7 +34,7 @@ struct DecodeParams {
     const int* token_list;    // tokens handled (nullptr: 0 .. n-1)
     float* part_o;            // [n, nq, splits, D]  (splits > 1)
     float* part_lse;          // [n, nq, splits]
-    int table_stride, nq, nkv, P, window, num_splits;
+    int table_stride, nq, nkv, logP, window, num_splits;
     float scale_log2;         // softmax scale * log2(e)
 };
 
@@ -39,8 +42,8 @@ template <int D>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const DecodeParams p) {
     constexpr int LDS = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* sK = reinterpret_cast<bf16*>(smem_raw);          // [2][CHUNK][LDS]
-    bf16* sV = sK + 2 * DEC_CHUNK * LDS;                   // [2][CHUNK][LDS]
+    bf16* sK = reinterpret_cast<bf16*>(smem_raw);          // [STAGES][CHUNK][LDS]
+    bf16* sV = sK + DEC_STAGES * DEC_CHUNK * LDS;          // [STAGES][CHUNK][LDS]
 
     const int kvh = blockIdx.x, split = blockIdx.y, ti = blockIdx.z;
     const int t = p.token_list ? p.token_list[ti] : ti;
@@ -81,23 +84,21 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     auto load_chunk = [&](int c, int stage) {
-        const int key0 = lo + c * DEC_CHUNK;
-        load_kv_rows<D, LDS, DEC_THREADS>(sK + stage * DEC_CHUNK * LDS, p.k_pages, table, key0, DEC_CHUNK, lo, hi,
-                                          p.P, p.nkv, kvh);
-        load_kv_rows<D, LDS, DEC_THREADS>(sV + stage * DEC_CHUNK * LDS, p.v_pages, table, key0, DEC_CHUNK, lo, hi,
-                                          p.P, p.nkv, kvh);
-        cp_async_commit();
+        if (c < c1)
+            load_kv_pair_rows<D, LDS, DEC_THREADS>(sK + stage * DEC_CHUNK * LDS, sV + stage * DEC_CHUNK * LDS,
+                                                   p.k_pages, p.v_pages, table, lo + c * DEC_CHUNK, DEC_CHUNK, lo, hi,
+                                                   p.logP, p.nkv, kvh);
+        cp_async_commit();      // a group per chunk slot, empty past the end, keeps the wait count fixed
     };
 
-    load_chunk(c0, 0);
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) load_chunk(c0 + s, s);
     for (int c = c0; c < c1; ++c) {
-        const int stage = (c - c0) & 1;
-        if (c + 1 < c1) {
-            load_chunk(c + 1, stage ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = (c - c0) % DEC_STAGES;
+        // the chunk that frees up is the one computed in the previous iteration (all warps passed
+        // the barrier at its end)
+        load_chunk(c + DEC_STAGES - 1, (c - c0 + DEC_STAGES - 1) % DEC_STAGES);
+        cp_async_wait<DEC_STAGES - 1>();
         __syncthreads();
         const int wkey0 = lo + c * DEC_CHUNK + warp * 16;     // first key of this warp's 16
         if (wkey0 < hi) {
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
         __syncthreads();
     }
 
+    cp_async_wait<0>();
     // Merge the four warps through shared memory (the K/V buffers are free now).
     l_run[0] = quad_sum(l_run[0]);
     l_run[1] = quad_sum(l_run[1]);
@@ -221,7 +223,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 template <int D>
 static int launch_decode(const DecodeParams& p, int n, cudaStream_t stream) {
     constexpr int LDS = D + 8;
-    const size_t kv_bytes = (size_t)2 * 2 * DEC_CHUNK * LDS * sizeof(bf16);
+    const size_t kv_bytes = (size_t)2 * DEC_STAGES * DEC_CHUNK * LDS * sizeof(bf16);
     const size_t merge_bytes = (size_t)(128 + 64 * D) * sizeof(float);
     const size_t smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
     static bool configured = false;
@@ -257,7 +259,9 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
     p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.block_table = block_table; p.page_base = page_base; p.token_row = token_row; p.positions = positions;
     p.token_list = token_list; p.part_o = part_o; p.part_lse = part_lse;
-    p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.P = P; p.window = window; p.num_splits = num_splits;
+    p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.logP = acorn_log2_exact(P);
+    if (p.logP < 0) return ACORN_ERR_UNSUPPORTED;   // page sizes are powers of two
+    p.window = window; p.num_splits = num_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
     int rc;
     switch (d) {

@@ -29,7 +29,7 @@ struct PrefillParams {
     const int* row_start;     // [rows + 1] offsets of the rows in the token arrays
     const int* row_pos;       // [rows] tokens of the request in the cache before the step
     const int* tiles;         // [n_tiles, 2]: row, first token of the tile relative to the row
-    int table_stride, nq, nkv, P, window;
+    int table_stride, nq, nkv, logP, window;
     float scale_log2;
 };
 
@@ -78,10 +78,8 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_kernel(const Pr
     const int n_chunks = (hi - lo + PRE_BN - 1) / PRE_BN;
     auto load_chunk = [&](int c, int stage) {
         const int key0 = lo + c * PRE_BN;
-        load_kv_rows<D, LDS, PRE_THREADS>(sK + stage * PRE_BN * LDS, p.k_pages, table, key0, PRE_BN, lo, hi, p.P,
-                                          p.nkv, kvh);
-        load_kv_rows<D, LDS, PRE_THREADS>(sV + stage * PRE_BN * LDS, p.v_pages, table, key0, PRE_BN, lo, hi, p.P,
-                                          p.nkv, kvh);
+        load_kv_pair_rows<D, LDS, PRE_THREADS>(sK + stage * PRE_BN * LDS, sV + stage * PRE_BN * LDS, p.k_pages,
+                                               p.v_pages, table, key0, PRE_BN, lo, hi, p.logP, p.nkv, kvh);
         cp_async_commit();
     };
 
@@ -212,7 +210,9 @@ extern "C" int acorn_attention_prefill(const void* q, int64_t q_stride, void* ou
     p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out;
     p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.block_table = block_table; p.page_base = page_base; p.row_start = row_start; p.row_pos = row_pos;
-    p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.P = P; p.window = window;
+    p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.logP = acorn_log2_exact(P);
+    if (p.logP < 0) return ACORN_ERR_UNSUPPORTED;   // page sizes are powers of two
+    p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     switch (d) {
         case 16: return launch_prefill<16>(p, n_tiles, stream);

@@ -51,10 +51,84 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid32, const T* __restr
     }
 }
 
+// The same with four elements per thread and step, the row kept in registers between the two
+// passes: for widths that are a multiple of 4 and at most threads * 4 * RMS_MAX_ITER.
+#define RMS_MAX_ITER 8
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid32, const T* __restrict__ delta,
+                                       const float* __restrict__ w, T* __restrict__ out,
+                                       const int* __restrict__ row_idx, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int64_t row = row_idx ? row_idx[r] : r;
+    const bool write_resid = (row_idx == nullptr) && (delta != nullptr);
+    float* x = resid32 + row * H;
+    const T* dl = delta ? delta + row * H : nullptr;
+    float4 v[RMS_MAX_ITER];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < RMS_MAX_ITER; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        if (i < H) {
+            float4 a = *reinterpret_cast<const float4*>(x + i);
+            if (dl) {
+                const float4 d = Vec4<T>::load(dl + i);
+                a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+            }
+            if (write_resid) *reinterpret_cast<float4*>(x + i) = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            v[it] = a;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    T* o = out + (int64_t)r * H;
+#pragma unroll
+    for (int it = 0; it < RMS_MAX_ITER; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        if (i < H) {
+            const float4 ww = *reinterpret_cast<const float4*>(w + i);
+            Vec4<T>::store(o + i, make_float4(v[it].x * inv * ww.x, v[it].y * inv * ww.y, v[it].z * inv * ww.z,
+                                              v[it].w * inv * ww.w));
+        }
+    }
+}
+
 extern "C" int acorn_add_rmsnorm(float* resid32, const void* delta, const float* w, void* out,
                                  const int* row_idx, int rows, int H, float eps, int dtype,
                                  cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (H % 4 == 0) {
+        int threads = ((H / 4 + 31) / 32) * 32;
+        if (threads > 256) threads = 256;
+        if ((int64_t)threads * 4 * RMS_MAX_ITER >= H) {
+            ACORN_DISPATCH_DTYPE(dtype, T, (add_rmsnorm_vec_kernel<T><<<rows, threads, 0, stream>>>(
+                resid32, (const T*)delta, w, (T*)out, row_idx, H, eps)));
+            return acorn_launch_status();
+        }
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     ACORN_DISPATCH_DTYPE(dtype, T, (add_rmsnorm_kernel<T><<<rows, threads, 0, stream>>>(
         resid32, (const T*)delta, w, (T*)out, row_idx, H, eps)));
@@ -75,9 +149,37 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores.
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int I8) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / I8;
+        const int i = (int)(idx - t * I8);
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + i) * 8);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + I8 + i) * 8);
+        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
+            __nv_bfloat162 o = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+            ow[k] = *reinterpret_cast<uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int dtype, cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * I;
     if (total <= 0) return 0;
+    if (dtype == ACORN_DTYPE_BF16 && I % 8 == 0) {
+        const int64_t total8 = total / 8;
+        int64_t blocks = (total8 + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        swiglu_bf16x8_kernel<<<(int)blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, total8, I / 8);
+        return acorn_launch_status();
+    }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     ACORN_DISPATCH_DTYPE(dtype, T, (swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>(

@@ -63,21 +63,54 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // Copies `rows` rows of D bf16 each (keys key0 .. key0+rows-1 of one kv head, looked up through
 // the block table) into shared memory with row stride LDS elements.  Keys outside [lo, hi) are
-// zero-filled.  `table` already points at logical page 0 of the row.
+// zero-filled.  `table` already points at logical page 0 of the row.  The page size is a power
+// of two, 1 << logP.
 template <int D, int LDS, int THREADS>
 __device__ __forceinline__ void load_kv_rows(bf16* sdst, const bf16* __restrict__ pages,
                                              const int* __restrict__ table, int key0, int rows, int lo, int hi,
-                                             int P, int nkv, int kvh) {
+                                             int logP, int nkv, int kvh) {
     constexpr int SEGS = D / 8;
+    const int pmask = (1 << logP) - 1;
     for (int idx = threadIdx.x; idx < rows * SEGS; idx += THREADS) {
         const int row = idx / SEGS, seg = idx - row * SEGS;
         const int key = key0 + row;
         const bool valid = key >= lo && key < hi;
         const bf16* src = pages;
         if (valid) {
-            const int page = table[key / P];
-            src = pages + (((int64_t)page * nkv + kvh) * P + (key % P)) * D + seg * 8;
+            const int page = __ldg(table + (key >> logP));
+            src = pages + (((((int64_t)page * nkv + kvh) << logP) + (key & pmask)) * D + seg * 8);
         }
         cp_async_16(smem_addr(sdst + row * LDS + seg * 8), src, valid);
     }
+}
+
+// The same for K and V together: a key's row has the same offset in both page tensors, so the
+// block-table lookup and the address arithmetic are done once for the pair.
+template <int D, int LDS, int THREADS>
+__device__ __forceinline__ void load_kv_pair_rows(bf16* sk, bf16* sv, const bf16* __restrict__ k_pages,
+                                                  const bf16* __restrict__ v_pages, const int* __restrict__ table,
+                                                  int key0, int rows, int lo, int hi, int logP, int nkv, int kvh) {
+    constexpr int SEGS = D / 8;
+    const int pmask = (1 << logP) - 1;
+    for (int idx = threadIdx.x; idx < rows * SEGS; idx += THREADS) {
+        const int row = idx / SEGS, seg = idx - row * SEGS;
+        const int key = key0 + row;
+        const bool valid = key >= lo && key < hi;
+        int64_t off = 0;
+        if (valid) {
+            const int page = __ldg(table + (key >> logP));
+            off = ((((int64_t)page * nkv + kvh) << logP) + (key & pmask)) * D + seg * 8;
+        }
+        const int soff = row * LDS + seg * 8;
+        cp_async_16(smem_addr(sk + soff), k_pages + off, valid);
+        cp_async_16(smem_addr(sv + soff), v_pages + off, valid);
+    }
+}
+
+// log2 of a power of two, -1 otherwise (host side).
+static inline int acorn_log2_exact(int v) {
+    if (v <= 0 || (v & (v - 1))) return -1;
+    int l = 0;
+    while ((1 << l) < v) ++l;
+    return l;
 }

@@ -38,7 +38,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 class ModelRunner:
     def __init__(self, config: ModelConfig, tensors: dict[str, torch.Tensor] | None, *, dtype: str = "bfloat16",
                  device: str = "cuda:0", num_blocks: int = 1024, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 8192, decoder: Decoder | None = None):
+                 max_step_tokens: int = 8192, decoder: Decoder | None = None, decode_graph: bool = True):
         ops.lib()      # fails here, loudly, if there is no device or no compiled kernels
         self.config = config
         self.dtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
@@ -55,6 +55,13 @@ class ModelRunner:
         self.max_step_tokens = max_step_tokens
         self.workspace = StepWorkspace(self.device)
         self.vocab_size = self.spec.vocab_size
+        # CUDA graphs of all-decode steps, keyed by the sizes that fix every launch of the step
+        self.decode_graph = decode_graph and self.decoder.graph_safe
+        self._graphs: dict[tuple, object] = {}
+        self._graph_seen: dict[tuple, int] = {}
+        self._graph_pool = None
+        self.graph_kernel_launches = 0
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ construction
 
@@ -114,7 +121,43 @@ class ModelRunner:
         plan = plan_step(entries, self.manager)
         self.last_plan = plan
         inputs = self.workspace.upload(plan)
-        logits = self.decoder.forward(inputs, self.caches)
+        if self.decode_graph and plan.all_decode:
+            logits = self._decode_step(plan, inputs)
+        else:
+            logits = self.decoder.forward(inputs, self.caches)
         for e in entries:
             self.manager.commit(e.cache, e.cache.length + len(e.tokens))
+        return logits
+
+    # ------------------------------------------------------------------ captured decode steps
+
+    def _decode_step(self, plan, inputs):
+        """An all-decode step: replayed from a CUDA graph once its shape has been seen twice.
+
+        The step arrays were just uploaded to the addresses the graph reads (the workspace's
+        layout is a function of the key), so a replay is this step.  The returned logits are
+        the graph's output buffer: valid until the next step."""
+        key = (plan.num_rows, plan.num_logits, tuple(g.block_table.shape[1] for g in plan.groups))
+        entry = self._graphs.get(key)
+        if entry is not None:
+            graph, logits, launches = entry
+            graph.replay()
+            self.graph_kernel_launches += launches
+            self.graph_replays += 1
+            return logits
+        seen = self._graph_seen.get(key, 0) + 1
+        self._graph_seen[key] = seen
+        logits = self.decoder.forward(inputs, self.caches)
+        if seen >= 2 and len(self._graphs) < 256:
+            # Capturing launches nothing: the eager run above is this step's result (and the warm-up).
+            before = ops.LAUNCHES
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.decoder.forward(inputs, self.caches)
+            launches = ops.LAUNCHES - before
+            ops.LAUNCHES = before
+            self._graphs[key] = (graph, out, launches)
         return logits

@@ -123,6 +123,11 @@ class Decoder:
             out.append(EntryCache(i, group, k, v, e.reads_cache_of is None, manager.state.get(i)))
         return out
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part allows a step to be captured and replayed (see ``Part.graph_safe``)."""
+        return all(getattr(part, "graph_safe", False) for _, part in self._named_parts)
+
     # ------------------------------------------------------------------ forward
 
     def forward(self, inputs, caches: list[EntryCache]) -> torch.Tensor | None:

@@ -24,6 +24,8 @@ from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, TensorSpec
 
 @MIXERS.register("attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, ctx: BuildContext, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: str | None, scale: float, qk_norm_eps: float | None = None,
                  window: int | None = None):

@@ -128,7 +128,15 @@ class CacheNeeds:
 
 
 class Part:
-    """Base of all parts: declares checkpoint tensors and takes them when loaded."""
+    """Base of all parts: declares checkpoint tensors and takes them when loaded.
+
+    ``graph_safe``: the part's ``forward`` only launches work whose shape follows from the
+    step's sizes (token count, row count, table stride) and reads everything else from device
+    arrays, so a step may be captured once in a CUDA graph and replayed for other steps of the
+    same sizes.  A part that looks at host-side values of the step leaves it False.
+    """
+
+    graph_safe = False
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Tensor names (relative to the part's prefix) -> spec."""

@@ -13,6 +13,8 @@ from .base import BLOCKS, Block
 
 @BLOCKS.register("prenorm")
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, ctx, mixer, feed_forward, norms):
         super().__init__(mixer, feed_forward, norms)
         missing = {"mixer", "feed_forward"} - set(norms)

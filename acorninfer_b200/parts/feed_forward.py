@@ -13,6 +13,8 @@ from .base import FEED_FORWARDS, BuildContext, FeedForward, TensorSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int):
         self.ctx = ctx
         self.hidden_size = hidden_size

@@ -16,6 +16,8 @@ from .base import NORMS, BuildContext, Norm, TensorSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, ctx: BuildContext, width: int, eps: float):
         self.ctx = ctx
         self.width = width
