@@ -1,0 +1,341 @@
+// out[M, N] = x[M, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05),
+// operands staged by TMA, accumulators in tensor memory.
+//
+// The weight matrix takes the 128-row side of the MMA ("swap-AB"): a CTA owns 128 rows of W
+// (output columns n0 .. n0+127) and MB tokens (MB = 16 .. 256), so that a decode step with few
+// tokens still fills the instruction and the kernel streams W once at memory speed.  Per
+// 64-element step along K, TMA brings a [128 x 64] tile of W and a [MB x 64] tile of x into a
+// ring of shared-memory stages (128-byte swizzle, K-major); one elected thread issues four
+// tcgen05.mma (M=128, N=MB, K=16) per stage into a [128 lanes x MB columns] float32 accumulator
+// in tensor memory; tcgen05.commit frees the stage.  When the K range is split (SPLITS > 1) the
+// CTAs of one output tile form a thread-block cluster, each reduces its share of K, and the
+// partial tiles are summed through distributed shared memory in a fixed order (deterministic,
+// no scratch in global memory).  The epilogue reads the accumulator with tcgen05.ld, lane =
+// output column, and writes out[m, n] as bfloat16 or float32.
+//
+// Every wait on an mbarrier is bounded: when a wait gives up, the kernel records where in
+// g_gemm_tc_error, skips the rest of its work, still frees its tensor memory and returns.
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+#define TC_BM 128            // rows of W per CTA (MMA M)
+#define TC_BK 64             // elements of K per stage (one 128-byte swizzle row)
+#define TC_THREADS 128
+#define TC_WAIT_LIMIT (1u << 22)
+
+__device__ int g_gemm_tc_error = 0;
+
+struct TcParams {
+    void* out;
+    int64_t ldo;
+    int M, N, K;
+    int kblocks;             // ceil(K / 64)
+    int out_f32;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+// Bounded wait for the phase with the given parity; false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t tries = 0; tries < TC_WAIT_LIMIT; ++tries) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred P1;\n mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n selp.u32 %0, 1, 0, P1;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups are
+// 1024 bytes apart (stride offset), descriptor version 1 (Blackwell), layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                       // leading offset: 1 (unused for swizzled K-major)
+    d |= (uint64_t)((1024 >> 4) & 0x3FFF) << 32;  // stride offset
+    d |= (uint64_t)1 << 46;                       // version
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ------------------------------------------------------------------ the kernel
+
+template <int MB, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                  const __grid_constant__ CUtensorMap map_x,
+                                                                  const TcParams p) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2;           // 16 KB
+    constexpr int B_BYTES = MB * TC_BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = MB < 32 ? 32 : MB;         // power of two >= 32 (MB is 16, 32, 64, 128 or 256)
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MB >> 3) << 17) |
+                               ((uint32_t)(TC_BM >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);   // full[S], empty[S], accum
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES), accum_bar = tc_smem(bars + 2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * MB;
+    const int splits = gridDim.z, split = blockIdx.z;
+    const int kb0 = (int)((int64_t)p.kblocks * split / splits), kb1 = (int)((int64_t)p.kblocks * (split + 1) / splits);
+    const int nkb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(tc_smem(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA loads into the ring
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1)) { atomicExch(&g_gemm_tc_error, 1); break; }
+            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            const uint32_t a = tc_smem(smem + s * STAGE_BYTES);
+            tma_load_2d(a, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
+            tma_load_2d(a + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, m0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1)) { atomicExch(&g_gemm_tc_error, 2); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a = tc_smem(smem + s * STAGE_BYTES);
+            const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)     // 16 elements = 32 bytes = 2 descriptor units along K
+                umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(empty0 + 8 * s);             // the stage is free once these MMAs have read it
+        }
+        umma_commit(accum_bar);                      // the accumulator is complete
+    }
+    __syncwarp();
+
+    // ---- epilogue: all four warps; warp w reads TMEM lanes 32w .. 32w+31 (output column n0 + 32w + lane)
+    if (nkb > 0) ok = mbar_wait(accum_bar, 0);
+    if (!ok) atomicExch(&g_gemm_tc_error, 3);
+    ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below is warp-wide
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int n = n0 + warp * 32 + lane;
+    const int m_valid = min(MB, p.M - m0);
+    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+    if (splits == 1) {
+#pragma unroll
+        for (int c = 0; c < MB; c += 16) {
+            float v[16];
+            if (ok && nkb > 0) {
+                tmem_ld16(taddr + c, v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            }
+            if (n < p.N) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int m = c + i;
+                    if (m < m_valid) {
+                        const int64_t o = (int64_t)(m0 + m) * p.ldo + n;
+                        if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = v[i];
+                        else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v[i]);
+                    }
+                }
+            }
+        }
+    } else {
+        // partial tile -> own shared memory [MB][128] float32 (the ring is drained: every stage
+        // was consumed before accum_bar completed), then a cluster-wide sum in rank order
+        float* part = reinterpret_cast<float*>(smem);
+#pragma unroll
+        for (int c = 0; c < MB; c += 16) {
+            float v[16];
+            if (ok && nkb > 0) {
+                tmem_ld16(taddr + c, v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) part[(c + i) * TC_BM + warp * 32 + lane] = v[i];
+        }
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
+        const int col = threadIdx.x;                                  // 128 threads = 128 columns
+        for (int m = rank; m < m_valid; m += csize) {
+            float acc = 0.f;
+            for (int q = 0; q < csize; ++q) acc += cluster.map_shared_rank(part, q)[m * TC_BM + col];
+            if (n0 + col < p.N) {
+                const int64_t o = (int64_t)(m0 + m) * p.ldo + n0 + col;
+                if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = acc;
+                else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(acc);
+            }
+        }
+        cluster.sync();        // peers may still be reading this CTA's partial tile
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, K] with row stride ld elements; box = [box_rows, 64] with 128-byte swizzle.
+// Elements outside the tensor read as zero.
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return ACORN_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
+}
+
+template <int MB, int STAGES>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
+    const size_t ring = (size_t)STAGES * STAGE_BYTES;
+    const size_t part = (size_t)MB * TC_BM * sizeof(float);
+    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MB, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.N + TC_BM - 1) / TC_BM, (p.M + MB - 1) / MB, splits);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<MB, STAGES>, mw, mx, p);
+    return e != cudaSuccess ? (int)e : acorn_launch_status();
+}
+
+// What the kernel takes: bf16 operands with K contiguous, K and both row strides multiples of 8
+// elements (16 bytes), 16-byte aligned bases, 1 <= splits <= 8.
+extern "C" int acorn_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw) {
+    return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && M <= (1 << 30);
+}
+
+extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
+                             int N, int K, int out_f32, int splits, cudaStream_t stream) {
+    if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
+    TcParams p;
+    p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.kblocks = (K + TC_BK - 1) / TC_BK; p.out_f32 = out_f32;
+    if (splits > p.kblocks) splits = p.kblocks;
+    const int mb = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, N, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, M, K, ldx, mb);
+    if (rc) return rc;
+    switch (mb) {
+        case 16: return launch_tc<16, 6>(mw, mx, p, splits, stream);
+        case 32: return launch_tc<32, 5>(mw, mx, p, splits, stream);
+        case 64: return launch_tc<64, 4>(mw, mx, p, splits, stream);
+        default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
+    }
+}
+
+// Reads and clears the flag that a bounded wait sets when it gives up (0 = no error).
+extern "C" int acorn_gemm_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_gemm_tc_error, &zero, sizeof(int));
+    return v;
+}

@@ -61,6 +61,10 @@ class _Sigs:
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                c_void_p]
     acorn_attention_prefill_supported = [c_int, c_int, c_int]
+    acorn_gemm_tc = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                     c_void_p]
+    acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
+    acorn_gemm_tc_error = []
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
     acorn_sample = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_void_p, c_void_p]
@@ -333,11 +337,60 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(lib().acorn_gemm_tc_supported(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))))
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    """Split of the K range (a cluster of that many CTAs per output tile): a power of two, at most
+    8, chosen so that a matrix with few 128-row tiles still puts one to two CTAs on every SM."""
+    tiles = -(-N // 128) * -(-M // (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128))
+    kblocks = -(-K // 64)
+    splits = 1
+    while splits < 8 and tiles * splits * 2 <= 2 * 148 and kblocks // (splits * 2) >= 4:
+        splits *= 2
+    return splits
+
+
+# At or below this many rows the tcgen05 kernel (weights on the 128-row side of the MMA) streams the
+# weight matrix at least as fast as the library product; above it the library's larger tiles win.
+GEMM_TC_MAX_ROWS = 64
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate)."""
+    if not gemm_tc_supported(x, w):
+        raise KernelError(f"gemm_tc does not take x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
+                          f"w {tuple(w.shape)} {w.dtype}: bf16, K contiguous, K and strides multiples of 8")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tc writes bfloat16 or float32")
+    M, K = x.shape
+    N = w.shape[0]
+    if splits is None:
+        splits = gemm_tc_splits(M, N, K)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(out, "out", out_dtype, 2)
+    _ok(lib().acorn_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+                            M, N, K, 1 if out_dtype == torch.float32 else 0, int(splits), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_error() -> int:
+    """0, or where a bounded wait inside the tcgen05 GEMM gave up since the last call (clears it)."""
+    return int(lib().acorn_gemm_tc_error())
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """x [T, K] times w [N, K] transposed.
 
     float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
-    bfloat16 operands: the library matrix product (cuBLAS), float32 accumulation;
+    bfloat16 operands: up to GEMM_TC_MAX_ROWS rows the tcgen05/TMA kernel of this library, above
+    that the library matrix product (cuBLAS); float32 accumulation either way, and
     ``out_dtype=float32`` keeps the accumulator's precision (used for logits).
     A weight stored in float32 under a bfloat16 engine is multiplied in float32.
     """
@@ -347,6 +400,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         return y if out_dtype == torch.float32 else cast(y, out_dtype)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtypes x={x.dtype}, w={w.dtype}")
+    if x.shape[0] <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w):
+        return gemm_tc(x, w, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())
