@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
     bf16* sK = reinterpret_cast<bf16*>(smem_raw);          // [STAGES][CHUNK][LDS]
     bf16* sV = sK + DEC_STAGES * DEC_CHUNK * LDS;          // [STAGES][CHUNK][LDS]
 
+    pdl_wait();
+    pdl_trigger();
     const int kvh = blockIdx.x, split = blockIdx.y, ti = blockIdx.z;
     const int t = p.token_list ? p.token_list[ti] : ti;
     const int r = p.token_row[t], pos = p.positions[t];
@@ -203,6 +205,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                               bf16* __restrict__ out, const int* __restrict__ token_list, int nq,
                                               int D, int num_splits) {
+    pdl_wait();
+    pdl_trigger();
     const int ti = blockIdx.x, head = blockIdx.y;
     const int t = token_list ? token_list[ti] : ti;
     const float* lse = part_lse + ((int64_t)ti * nq + head) * num_splits;
@@ -234,8 +238,7 @@ static int launch_decode(const DecodeParams& p, int n, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(p.nkv, p.num_splits, n);
-    attention_decode_kernel<D><<<grid, DEC_THREADS, smem, stream>>>(p);
-    return acorn_launch_status();
+    return acorn_launch(attention_decode_kernel<D>, grid, dim3(DEC_THREADS), smem, stream, p);
 }
 
 // Sizes this kernel takes: head_dim a multiple of 16 up to 128, or 256; nq / nkv <= 16.
@@ -278,7 +281,6 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
     }
     if (rc != 0 || num_splits == 1) return rc;
     dim3 grid(n, nq);
-    attention_decode_merge_kernel<<<grid, d >= 128 ? 128 : 64, 0, stream>>>(part_o, part_lse, (bf16*)out, token_list,
-                                                                           nq, d, num_splits);
-    return acorn_launch_status();
+    return acorn_launch(attention_decode_merge_kernel, grid, dim3(d >= 128 ? 128 : 64), 0, stream,
+                        (const float*)part_o, (const float*)part_lse, (bf16*)out, token_list, nq, d, num_splits);
 }

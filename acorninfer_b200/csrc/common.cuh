@@ -77,3 +77,40 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     } while (0)
 
 static inline int acorn_launch_status() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of this library is launched with programmatic stream serialization: it may be
+// scheduled while the kernel before it in the stream is still running, and must call
+// pdl_wait() before it touches global memory that an earlier kernel wrote or still reads
+// (after the wait, the earlier kernel has completed and its writes are visible).  pdl_trigger()
+// lets the kernel after this one be scheduled.  Launched without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+
+static inline bool acorn_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = std::getenv("ACORN_PDL");
+        on = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int acorn_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = acorn_pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}

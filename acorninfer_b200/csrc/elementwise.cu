@@ -6,6 +6,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out32, int H) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const T* row = table + (int64_t)ids[t] * H;
     float* o = out32 + (int64_t)t * H;
@@ -15,8 +17,8 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
 extern "C" int acorn_embed(const int* ids, const void* table, float* out32, int tokens, int H,
                            int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    ACORN_DISPATCH_DTYPE(dtype, T, (embed_kernel<T><<<tokens, 256, 0, stream>>>(ids, (const T*)table, out32, H)));
-    return acorn_launch_status();
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(embed_kernel<T>, dim3(tokens), dim3(256), 0, stream, ids, (const T*)table, out32, H));
+    return ACORN_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- add + RMSNorm
@@ -29,6 +31,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid32, const T* __restr
                                    const float* __restrict__ w, T* __restrict__ out,
                                    const int* __restrict__ row_idx, int H, float eps) {
     __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const int64_t row = row_idx ? row_idx[r] : r;
     const bool write_resid = (row_idx == nullptr) && (delta != nullptr);
@@ -81,6 +85,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid32, const T* __r
                                        const float* __restrict__ w, T* __restrict__ out,
                                        const int* __restrict__ row_idx, int H, float eps) {
     __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const int64_t row = row_idx ? row_idx[r] : r;
     const bool write_resid = (row_idx == nullptr) && (delta != nullptr);
@@ -124,21 +130,23 @@ extern "C" int acorn_add_rmsnorm(float* resid32, const void* delta, const float*
         int threads = ((H / 4 + 31) / 32) * 32;
         if (threads > 256) threads = 256;
         if ((int64_t)threads * 4 * RMS_MAX_ITER >= H) {
-            ACORN_DISPATCH_DTYPE(dtype, T, (add_rmsnorm_vec_kernel<T><<<rows, threads, 0, stream>>>(
-                resid32, (const T*)delta, w, (T*)out, row_idx, H, eps)));
-            return acorn_launch_status();
+            ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(add_rmsnorm_vec_kernel<T>, dim3(rows), dim3(threads), 0,
+                                                               stream, resid32, (const T*)delta, w, (T*)out, row_idx,
+                                                               H, eps));
         }
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    ACORN_DISPATCH_DTYPE(dtype, T, (add_rmsnorm_kernel<T><<<rows, threads, 0, stream>>>(
-        resid32, (const T*)delta, w, (T*)out, row_idx, H, eps)));
-    return acorn_launch_status();
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, stream,
+                                                       resid32, (const T*)delta, w, (T*)out, row_idx, H, eps));
+    return ACORN_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i],   silu(z) = z / (1 + exp(-z))
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I) {
+    pdl_wait();
+    pdl_trigger();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / I;
@@ -151,6 +159,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 // bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores.
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int I8) {
+    pdl_wait();
+    pdl_trigger();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / I8;
@@ -177,14 +187,14 @@ extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int dt
         const int64_t total8 = total / 8;
         int64_t blocks = (total8 + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        swiglu_bf16x8_kernel<<<(int)blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, total8, I / 8);
-        return acorn_launch_status();
+        return acorn_launch(swiglu_bf16x8_kernel, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
+                            total8, I / 8);
     }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    ACORN_DISPATCH_DTYPE(dtype, T, (swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>(
-        (const T*)gu, (T*)out, total, I)));
-    return acorn_launch_status();
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                       (const T*)gu, (T*)out, total, I));
+    return ACORN_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- casts

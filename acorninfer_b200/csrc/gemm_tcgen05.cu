@@ -13,6 +13,10 @@
 // no scratch in global memory).  The epilogue reads the accumulator with tcgen05.ld, lane =
 // output column, and writes out[m, n] as bfloat16 or float32.
 //
+// The kernel is launched with programmatic stream serialization: the weight tiles of the first
+// stages are requested before griddepcontrol.wait, so the weights start to stream while the
+// kernel before this one finishes; everything that depends on earlier kernels comes after it.
+//
 // Every wait on an mbarrier is bounded: when a wait gives up, the kernel records where in
 // g_gemm_tc_error, skips the rest of its work, still frees its tensor memory and returns.
 #include <cooperative_groups.h>
@@ -146,8 +150,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     bool ok = true;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: TMA loads into the ring
-        for (int i = 0; i < nkb; ++i) {
+        // ---- producer: TMA loads into the ring.  The weight tiles of the first stages do not
+        // depend on the kernel before this one, so they are requested before pdl_wait(): the
+        // weights stream while the previous kernel drains.  The token tiles (and every later
+        // stage) come after the wait.
+        const int pre = nkb < STAGES ? nkb : STAGES;
+        for (int i = 0; i < pre; ++i) {
+            mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+            tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(tc_smem(smem + i * STAGE_BYTES) + A_BYTES, &map_x, full0 + 8 * i, (kb0 + i) * TC_BK, m0);
+        for (int i = pre; i < nkb; ++i) {
             const int s = i % STAGES;
             if (!mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1)) { atomicExch(&g_gemm_tc_error, 1); break; }
             mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
@@ -173,6 +188,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     __syncwarp();
 
     // ---- epilogue: all four warps; warp w reads TMEM lanes 32w .. 32w+31 (output column n0 + 32w + lane)
+    pdl_wait();          // the output buffer may still be read by the kernel before this one
+    pdl_trigger();
     if (nkb > 0) ok = mbar_wait(accum_bar, 0);
     if (!ok) atomicExch(&g_gemm_tc_error, 3);
     ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below is warp-wide
@@ -294,13 +311,15 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = acorn_pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<MB, STAGES>, mw, mx, p);
     return e != cudaSuccess ? (int)e : acorn_launch_status();
 }

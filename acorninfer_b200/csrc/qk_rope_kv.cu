@@ -23,6 +23,8 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
                                   int tokens, int nq, int nkv, int d, int rot, int pairing, int P,
                                   float eps, int write_kv) {
     extern __shared__ float smem[];
+    pdl_wait();
+    pdl_trigger();
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = write_kv ? (nq + 2 * nkv) : nq;
@@ -85,8 +87,9 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
     const int64_t items = (int64_t)tokens * heads;
     const int64_t blocks = (items + warps - 1) / warps;
     const size_t smem = (size_t)warps * d * sizeof(float);
-    ACORN_DISPATCH_DTYPE(dtype, T, (qk_rope_kv_kernel<T><<<(unsigned)blocks, warps * 32, smem, stream>>>(
-        (T*)qkv, q_w, k_w, inv_freq, positions, token_row, block_table, page_base, table_stride,
-        (T*)k_pages, (T*)v_pages, tokens, nq, nkv, d, rot, pairing, P, eps, write_kv)));
-    return acorn_launch_status();
+    ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(
+        qk_rope_kv_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, (T*)qkv, q_w, k_w, inv_freq,
+        positions, token_row, block_table, page_base, table_stride, (T*)k_pages, (T*)v_pages, tokens, nq, nkv, d, rot,
+        pairing, P, eps, write_kv));
+    return ACORN_ERR_UNSUPPORTED;
 }

@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     __shared__ unsigned int uscratch[32];
     __shared__ float seg_prefix[SAMPLE_THREADS / 32];
     __shared__ int s_found;
+    pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* x = logits + (int64_t)r * ld;
     const float temp = temperature[r];
@@ -175,9 +177,8 @@ extern "C" int acorn_sample(const float* logits, int64_t ld, int rows, int V, co
                             const unsigned long long* counter, int* token_out, float* logprob_out,
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, seed,
-                                                       counter, token_out, logprob_out);
-    return acorn_launch_status();
+    return acorn_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature, top_k,
+                        top_p, seed, counter, token_out, logprob_out);
 }
 
 // Host copy of the generator, for callers that need the same uniforms off the device.

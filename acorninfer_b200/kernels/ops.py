@@ -357,7 +357,7 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
 
 # At or below this many rows the tcgen05 kernel (weights on the 128-row side of the MMA) streams the
 # weight matrix at least as fast as the library product; above it the library's larger tiles win.
-GEMM_TC_MAX_ROWS = 64
+GEMM_TC_MAX_ROWS = 32
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
