@@ -202,25 +202,36 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 }
 
 // Merges the splits of one (token, head): out = sum_s w_s o_s / sum_s w_s, w_s = 2^(lse_s - max lse).
+// The first warp turns the (at most 32) log-sum-exps into weights; then each thread sums its
+// head dimensions over the splits.
+#define DEC_MAX_SPLITS 32
+
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                               bf16* __restrict__ out, const int* __restrict__ token_list, int nq,
                                               int D, int num_splits) {
+    __shared__ float wgt[DEC_MAX_SPLITS];
     pdl_wait();
     pdl_trigger();
     const int ti = blockIdx.x, head = blockIdx.y;
     const int t = token_list ? token_list[ti] : ti;
-    const float* lse = part_lse + ((int64_t)ti * nq + head) * num_splits;
-    float mx = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, lse[s]);
-    float wsum = 0.f;
-    for (int s = 0; s < num_splits; ++s) wsum += exp2f(lse[s] - mx);
+    const int64_t slot0 = ((int64_t)ti * nq + head) * num_splits;
+    if (threadIdx.x < 32) {
+        const float lse = threadIdx.x < num_splits ? part_lse[slot0 + threadIdx.x] : -INFINITY;
+        const float mx = warp_max(lse);
+        const float w = exp2f(lse - mx);                    // an empty split: exp2(-inf) = 0
+        const float wsum = warp_sum(w);
+        if (threadIdx.x < num_splits) wgt[threadIdx.x] = w / wsum;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float acc = 0.f;
+#pragma unroll 4
         for (int s = 0; s < num_splits; ++s) {
-            const float w = exp2f(lse[s] - mx);
-            if (w > 0.f) acc += w * part_o[(((int64_t)ti * nq + head) * num_splits + s) * D + i];
+            const float w = wgt[s];
+            const float v = part_o[(slot0 + s) * D + i];
+            acc += w > 0.f ? w * v : 0.f;                   // an empty split left its slot unwritten
         }
-        out[((int64_t)t * nq + head) * D + i] = __float2bfloat16_rn(acc / wsum);
+        out[((int64_t)t * nq + head) * D + i] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -254,7 +265,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
                                       int window, int num_splits, float* part_o, float* part_lse,
                                       cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (!acorn_attention_decode_supported(nq, nkv, d) || num_splits < 1 || num_splits > 65535 || n > 65535)
+    if (!acorn_attention_decode_supported(nq, nkv, d) || num_splits < 1 || num_splits > DEC_MAX_SPLITS || n > 65535)
         return ACORN_ERR_UNSUPPORTED;
     if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return ACORN_ERR_UNSUPPORTED;
     DecodeParams p;

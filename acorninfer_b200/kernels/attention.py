@@ -18,12 +18,12 @@ _CHUNK = 64
 
 
 def decode_splits(rows: int, num_kv_heads: int, key_bound: int) -> int:
-    """Splits of the key range so that rows * kv heads * splits CTAs fill the GPU.  ``key_bound``
+    """Splits of the key range so that rows * kv heads * splits CTAs fill the GPU in one wave
+    (two CTAs of the decode kernel fit on an SM), never more CTAs than that.  ``key_bound``
     bounds the keys any row reads; it changes only with the table stride, so a captured step
     keeps its grid."""
     ctas = max(1, rows * num_kv_heads)
-    want = -(-_TARGET_CTAS // ctas)
-    return max(1, min(want, -(-key_bound // _CHUNK), 64))
+    return max(1, min(_TARGET_CTAS // ctas, -(-key_bound // _CHUNK), 32))
 
 
 def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, d: int, scale: float,

@@ -272,7 +272,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
     _check(v_pages, "v_pages", q.dtype, 4)
     _check(block_table, "block_table", torch.int32, 2)
     n = num_tokens if token_list is None else token_list.numel()
-    if n > 65535 or not (1 <= num_splits <= 65535):
+    if n > 65535 or not (1 <= num_splits <= 32):
         raise KernelError(f"attention_decode: {n} tokens / {num_splits} splits beyond the grid limits")
     if out is None:
         out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)

@@ -150,7 +150,7 @@ BF16_TOL = dict(atol=2e-2, rtol=2e-2)
 @pytest.mark.parametrize("nq,nkv,d,P,window", [(32, 8, 128, 16, None), (4, 2, 16, 4, None), (8, 1, 32, 8, None),
                                                (10, 2, 48, 16, None), (6, 3, 80, 8, 50), (16, 1, 64, 32, None),
                                                (5, 5, 112, 16, 129), (4, 2, 256, 16, None)])
-@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("splits", [1, 3, 32])
 def test_attention_decode_kernel(nq, nkv, d, P, window, splits):
     before = [0, 1, 63, 64, 65, 700, 127, 2000]           # one key; page and chunk edges; long rows
     qlens = [1] * len(before)
