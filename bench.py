@@ -213,11 +213,84 @@ def time_e2e(runner, B: int, steps: int, warmup: int, ctx_end: int, torch):
 
 
 def reference_arm(args) -> int:
+    """The unmodified reference (installed under baseline/_ref) through its own public API:
+    ``from_pretrained`` + ``Engine.submit/step`` with its fastest documented settings (Triton paged
+    attention, fused ops, CUDA graph for decode).  Same metric and sizes: batch 8, context 4,096,
+    Qwen3-8B layer sizes, random weights written to a temporary folder first."""
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "acorninfer").is_dir():
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this box"}))
         return 0
-    print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired yet"}))
+    import shutil
+    import tempfile
+    tmp = Path(tempfile.mkdtemp(prefix="acorn_ref_model_"))
+    try:
+        import torch
+
+        from acorninfer_b200.config.model_config import Qwen3Config, dump_config
+        from acorninfer_b200.models.decoder import expected_tensors
+        from acorninfer_b200.registry import spec_for
+        from acorninfer_b200.weights.random_init import random_state
+        from acorninfer_b200.weights.safetensors_io import write_safetensors
+
+        conf = dict(QWEN3_8B, num_hidden_layers=args.layers, bos_token_id=0, eos_token_id=(151645,))
+        cfg = Qwen3Config(**conf)
+        dump_config(cfg, tmp)
+        tensors = random_state(expected_tensors(spec_for(cfg)), 0, 0.02, 0.0, torch.bfloat16, "cuda:0")
+        tensors = {k: v.cpu() for k, v in tensors.items()}
+        write_safetensors(tmp / "model.safetensors", tensors)
+        (tmp / "model.safetensors.index.json").write_text(json.dumps(
+            {"weight_map": {k: "model.safetensors" for k in tensors}}))
+        del tensors
+        torch.cuda.empty_cache()
+
+        sys.path.insert(0, str(ref))
+        from acorninfer.engine.engine import Engine as RefEngine
+        from acorninfer.models.qwen3 import from_pretrained
+        from acorninfer.sampler import SamplingParams as RefParams
+
+        model = from_pretrained(str(tmp), "cuda:0", torch.bfloat16)
+        model.attention_backend = "triton"
+        model.fused_ops = True
+        model.decode_graph = True
+        B, steps, warmup = args.batch, args.steps, max(args.warmup, 3)
+        engine = RefEngine(model, None, num_blocks=B * CONTEXT // PAGE + 64, page_size=PAGE, max_running=B,
+                           watermark_blocks=8)
+        prompt_len = CONTEXT - steps - warmup - 1
+        g = torch.Generator().manual_seed(100 + B)
+        prompts = torch.randint(0, QWEN3_8B["vocab_size"], (B, prompt_len), generator=g).tolist()
+        for p in prompts:
+            engine.submit(p, RefParams(temperature=0.0), max_tokens=steps + warmup + 1, eos_ids=frozenset())
+        while any(not engine.seqs[i].generated_ids for i in engine.seqs):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        clocks = ClockSampler()
+        clocks.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        produced = 0
+        for _ in range(steps):
+            produced += len(engine.step())
+        end.record()
+        torch.cuda.synchronize()
+        ms = max(start.elapsed_time(end), (time.perf_counter() - t0) * 1e3)
+        clock_info = clocks.stop()
+        line = {"impl": "reference", "metric": "decode tok/s at batch 8, context 4096 (Qwen3-8B layer sizes, 1 B200)",
+                "value": round(produced / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+                "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"model": "Qwen3-8B sizes, random weights", "layers": args.layers, "global_batch": B,
+                           "seq_len": CONTEXT, "page_size": PAGE, "settings": "triton attention, fused ops, decode graph"},
+                "e2e": {"value": round(produced / (ms / 1e3), 1), "unit": "tokens/s"}, "clocks": clock_info}
+        print(json.dumps(line))
+    except Exception as exc:  # the reference could not run here: say why, in one line
+        reason = f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
     return 0
 
 
