@@ -1,0 +1,124 @@
+"""Times one kernel of the library alone, at given sizes, with CUDA events.
+
+    python -m acorninfer_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096
+    python -m acorninfer_b200.kernels.microbench attn-decode --batch 64 --context 4096
+    python -m acorninfer_b200.kernels.microbench attn-prefill --tokens 2048
+
+Prints the time per call and the achieved GB/s (bytes the kernel must read) or TFLOPS.
+Inputs are larger than L2 or rotated over several copies, so DRAM figures mean something;
+calls are captured in a CUDA graph so that host launch time is not measured.  The same
+command under ``ncu`` profiles the kernel (few launches: ``--reps 2 --graph 0``).
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import ops
+from .attention import decode_splits
+
+DEV = "cuda:0"
+
+
+def _time(fns, reps: int, graph: bool) -> float:
+    """Microseconds per call of the callables in ``fns`` (cycled)."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(reps):
+                fns[i % len(fns)]()
+        g.replay()
+        torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    if graph:
+        g.replay()
+    else:
+        for i in range(reps):
+            fns[i % len(fns)]()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / reps * 1e3
+
+
+def bench_gemm(a) -> None:
+    copies = max(2, int(400e6 // (a.n * a.k * 2)) + 1)
+    ws = [torch.randn(a.n, a.k, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(a.m, a.k, device=DEV, dtype=torch.bfloat16)
+    splits = a.splits or ops.gemm_tc_splits(a.m, a.n, a.k)
+    us = _time([lambda w=w: ops.gemm_tc(x, w, torch.bfloat16, splits=splits) for w in ws], a.reps, a.graph)
+    lib = _time([lambda w=w: torch.mm(x, w.t()) for w in ws], a.reps, a.graph) if a.library else float("nan")
+    gb, fl = a.n * a.k * 2 / 1e9, 2.0 * a.m * a.n * a.k
+    print(f"gemm_tcgen05 M={a.m} N={a.n} K={a.k} splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of weights, "
+          f"{fl / us / 1e6:.1f} TFLOPS; library product {lib:.1f} us; error flag {ops.gemm_tc_error()}")
+
+
+def bench_attn_decode(a) -> None:
+    nq, nkv, d, P, B, ctx = a.heads, a.kv_heads, a.head_dim, a.page, a.batch, a.context
+    pages_per = ctx // P
+    k_pages = torch.randn(B * pages_per, nkv, P, d, device=DEV, dtype=torch.bfloat16)
+    v_pages = torch.randn_like(k_pages)
+    table = torch.randperm(B * pages_per, device=DEV).to(torch.int32).view(B, pages_per).contiguous()
+    base = torch.zeros(B, dtype=torch.int32, device=DEV)
+    rows = torch.arange(B, dtype=torch.int32, device=DEV)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
+    qkv = torch.randn(B, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
+    splits = a.splits or decode_splits(B, nkv, ctx)
+    us = _time([lambda: ops.attention_decode(qkv, qkv.stride(0), k_pages, v_pages, table, base, rows, pos, B, nq, nkv,
+                                             d, d ** -0.5, None, splits)], a.reps, a.graph)
+    gb = B * ctx * nkv * d * 2 * 2 / 1e9
+    print(f"attention_decode B={B} context={ctx} heads={nq}/{nkv} d={d} page={P} splits={splits}: {us:.1f} us, "
+          f"{gb / us * 1e6:.0f} GB/s of K and V")
+
+
+def bench_attn_prefill(a) -> None:
+    nq, nkv, d, P, T = a.heads, a.kv_heads, a.head_dim, a.page, a.tokens
+    pages = -(-T // P)
+    k_pages = torch.randn(pages, nkv, P, d, device=DEV, dtype=torch.bfloat16)
+    v_pages = torch.randn_like(k_pages)
+    table = torch.randperm(pages, device=DEV).to(torch.int32).view(1, pages).contiguous()
+    base = torch.zeros(1, dtype=torch.int32, device=DEV)
+    row_start = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    row_pos = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([(0, q0) for q0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
+    us = _time([lambda: ops.attention_prefill(qkv, qkv.stride(0), k_pages, v_pages, table, base, row_start, row_pos,
+                                              tiles, T, nq, nkv, d, d ** -0.5, None)], a.reps, a.graph)
+    fl = nq * d * 4.0 * (T * (T + 1) / 2)
+    print(f"attention_prefill tokens={T} heads={nq}/{nkv} d={d} page={P}: {us:.1f} us, {fl / us / 1e6:.0f} TFLOPS (causal)")
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="microbench")
+    sub = p.add_subparsers(dest="what", required=True)
+    common = argparse.ArgumentParser(add_help=False)
+    common.add_argument("--reps", type=int, default=20)
+    common.add_argument("--graph", type=int, default=1, help="1: time a CUDA graph of the calls; 0: plain launches")
+    g = sub.add_parser("gemm", parents=[common])
+    g.add_argument("--m", type=int, default=8)
+    g.add_argument("--n", type=int, default=24576)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--splits", type=int, default=0)
+    g.add_argument("--library", type=int, default=1, help="also time the library product")
+    for name in ("attn-decode", "attn-prefill"):
+        s = sub.add_parser(name, parents=[common])
+        s.add_argument("--heads", type=int, default=32)
+        s.add_argument("--kv-heads", type=int, default=8)
+        s.add_argument("--head-dim", type=int, default=128)
+        s.add_argument("--page", type=int, default=16)
+        s.add_argument("--batch", type=int, default=64)
+        s.add_argument("--context", type=int, default=4096)
+        s.add_argument("--tokens", type=int, default=2048)
+        s.add_argument("--splits", type=int, default=0)
+    a = p.parse_args(argv)
+    {"gemm": bench_gemm, "attn-decode": bench_attn_decode, "attn-prefill": bench_attn_prefill}[a.what](a)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
