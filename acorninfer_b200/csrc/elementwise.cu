@@ -142,31 +142,36 @@ extern "C" int acorn_add_rmsnorm(float* resid32, const void* delta, const float*
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i],   silu(z) = z / (1 + exp(-z))
+// out[t, i] = silu(gate) * up,   silu(z) = z / (1 + exp(-z)).  A row of gu holds, per block of b
+// outputs, b gate values then b up values: gate of output i at (i / b) * 2b + i % b, up b further.
+// b = I is the plain layout [gate | up].
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int I, int b) {
     pdl_wait();
     pdl_trigger();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / I;
         const int i = (int)(idx - t * I);
-        const float g = to_float(gu[t * 2 * I + i]);
-        const float u = to_float(gu[t * 2 * I + I + i]);
+        const int64_t gi = t * 2 * I + (int64_t)(i / b) * 2 * b + i % b;
+        const float g = to_float(gu[gi]);
+        const float u = to_float(gu[gi + b]);
         out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
-// bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores.
-__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int I8) {
+// bfloat16 rows whose block width b is a multiple of 8: 16-byte loads and stores (b8 = b / 8).
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int I8,
+                                     int b8) {
     pdl_wait();
     pdl_trigger();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / I8;
         const int i = (int)(idx - t * I8);
-        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + i) * 8);
-        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + I8 + i) * 8);
+        const int64_t gi = t * 2 * I8 + (int64_t)(i / b8) * 2 * b8 + i % b8;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + gi * 8);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (gi + b8) * 8);
         const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
         uint32_t ow[4];
 #pragma unroll
@@ -180,20 +185,22 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int dtype, cudaStream_t stream) {
+extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int block, int dtype,
+                            cudaStream_t stream) {
     const int64_t total = (int64_t)tokens * I;
     if (total <= 0) return 0;
-    if (dtype == ACORN_DTYPE_BF16 && I % 8 == 0) {
+    if (block <= 0 || I % block != 0) return ACORN_ERR_UNSUPPORTED;
+    if (dtype == ACORN_DTYPE_BF16 && block % 8 == 0) {
         const int64_t total8 = total / 8;
         int64_t blocks = (total8 + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
         return acorn_launch(swiglu_bf16x8_kernel, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
-                            total8, I / 8);
+                            total8, I / 8, block / 8);
     }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     ACORN_DISPATCH_DTYPE(dtype, T, return acorn_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
-                                                       (const T*)gu, (T*)out, total, I));
+                                                       (const T*)gu, (T*)out, total, I, block));
     return ACORN_ERR_UNSUPPORTED;
 }
 

@@ -33,12 +33,26 @@ namespace cg = cooperative_groups;
 
 __device__ int g_gemm_tc_error = 0;
 
+#define TC_MODE_PLAIN 0       // out = product
+#define TC_MODE_ADD_NORM 1    // residual += product; out = bf16(residual * norm_w); ss_out = partial sum of squares
+#define TC_MODE_SWIGLU 2      // tiles of 64 gate + 64 up columns: out = silu(gate) * up
+
 struct TcParams {
     void* out;
     int64_t ldo;
     int M, N, K;
     int kblocks;             // ceil(K / 64)
     int out_f32;
+    int mode;
+    // rows of x that still lack their factor rsqrt(mean(residual^2) + eps): partial sums of squares
+    const float* ss_in;      // [ss_parts, M] or nullptr
+    int ss_parts, norm_width;
+    float eps;
+    // TC_MODE_ADD_NORM
+    float* resid;            // [M, ldr] float32, updated in place
+    int64_t ldr;
+    const float* norm_w;     // [N]
+    float* ss_out;           // [ceil(N / 128), M]
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -198,59 +212,108 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     const int m_valid = min(MB, p.M - m0);
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
-    if (splits == 1) {
+    // The accumulator tile goes to this CTA's shared memory as [MB][128] float32 (the ring is
+    // drained: every stage was consumed before accum_bar completed).  With a split K range the
+    // tiles of the cluster's CTAs are then summed in rank order, each CTA finishing the rows
+    // m = rank, rank + csize, ...; without a split the CTA finishes all rows of its own tile.
+    float* part = reinterpret_cast<float*>(smem);
+    float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // [4 warps][MB] + inv[MB]
+    float* inv_s = red + 4 * MB;
 #pragma unroll
-        for (int c = 0; c < MB; c += 16) {
-            float v[16];
-            if (ok && nkb > 0) {
-                tmem_ld16(taddr + c, v);
-            } else {
+    for (int c = 0; c < MB; c += 16) {
+        float v[16];
+        if (ok && nkb > 0) {
+            tmem_ld16(taddr + c, v);
+        } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) part[(c + i) * TC_BM + warp * 32 + lane] = v[i];
+    }
+    // Rows of x that arrive un-normalised (x = residual * norm weight): the factor
+    // rsqrt(mean(residual^2) + eps) of each row is applied to the product here.
+    if (threadIdx.x < MB) {
+        float f = 1.f;
+        if (p.ss_in != nullptr && m0 + (int)threadIdx.x < p.M) {
+            float ss = 0.f;
+            for (int q = 0; q < p.ss_parts; ++q) ss += p.ss_in[(int64_t)q * p.M + m0 + threadIdx.x];
+            f = rsqrtf(ss / (float)p.norm_width + p.eps);
+        }
+        inv_s[threadIdx.x] = f;
+    }
+    int rank = 0, csize = 1;
+    if (splits > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        rank = (int)cluster.block_rank();
+        csize = (int)cluster.num_blocks();
+    } else {
+        __syncthreads();
+    }
+    const int col = threadIdx.x;                                      // 128 threads = 128 columns of the tile
+    auto tile_sum = [&](int m, int c) -> float {
+        if (splits == 1) return part[m * TC_BM + c];
+        cg::cluster_group cluster = cg::this_cluster();
+        float acc = 0.f;
+        for (int q = 0; q < csize; ++q) acc += cluster.map_shared_rank(part, q)[m * TC_BM + c];
+        return acc;
+    };
+    if (p.mode == TC_MODE_PLAIN) {
+        for (int m = rank; m < m_valid; m += csize) {
+            const float val = tile_sum(m, col) * inv_s[m];
+            if (n0 + col < p.N) {
+                const int64_t o = (int64_t)(m0 + m) * p.ldo + n0 + col;
+                if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = val;
+                else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
             }
-            if (n < p.N) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int m = c + i;
-                    if (m < m_valid) {
-                        const int64_t o = (int64_t)(m0 + m) * p.ldo + n;
-                        if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = v[i];
-                        else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v[i]);
-                    }
-                }
+        }
+    } else if (p.mode == TC_MODE_SWIGLU) {
+        // the tile holds 64 gate columns, then the 64 up columns of the same outputs
+        for (int m = rank; m < m_valid; m += csize) {
+            if (col < 64) {
+                const float g = tile_sum(m, col) * inv_s[m], u = tile_sum(m, col + 64) * inv_s[m];
+                const int oc = blockIdx.x * 64 + col;
+                if (oc < p.N / 2)
+                    reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + oc] =
+                        __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
             }
         }
     } else {
-        // partial tile -> own shared memory [MB][128] float32 (the ring is drained: every stage
-        // was consumed before accum_bar completed), then a cluster-wide sum in rank order
-        float* part = reinterpret_cast<float*>(smem);
+        // TC_MODE_ADD_NORM: residual += product; out = bf16(residual * norm weight), not yet
+        // scaled; this tile's share of sum(residual^2) per row goes to ss_out[tile][row]
+        constexpr int MAX_ROWS = MB <= 32 ? MB : 1;     // the host refuses this mode for larger tiles
+        float sq[MAX_ROWS];
 #pragma unroll
-        for (int c = 0; c < MB; c += 16) {
-            float v[16];
-            if (ok && nkb > 0) {
-                tmem_ld16(taddr + c, v);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) part[(c + i) * TC_BM + warp * 32 + lane] = v[i];
-        }
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
-        const int col = threadIdx.x;                                  // 128 threads = 128 columns
-        for (int m = rank; m < m_valid; m += csize) {
-            float acc = 0.f;
-            for (int q = 0; q < csize; ++q) acc += cluster.map_shared_rank(part, q)[m * TC_BM + col];
-            if (n0 + col < p.N) {
-                const int64_t o = (int64_t)(m0 + m) * p.ldo + n0 + col;
-                if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = acc;
-                else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(acc);
+        for (int i = 0; i < MAX_ROWS; ++i) {
+            sq[i] = 0.f;
+            const int m = rank + i * csize;
+            if (m < m_valid) {
+                const float val = tile_sum(m, col) * inv_s[m];
+                if (n0 + col < p.N) {
+                    const int64_t ri = (int64_t)(m0 + m) * p.ldr + n0 + col;
+                    const float r = p.resid[ri] + val;
+                    p.resid[ri] = r;
+                    reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + n0 + col] =
+                        __float2bfloat16_rn(r * p.norm_w[n0 + col]);
+                    sq[i] = r * r;
+                }
             }
         }
-        cluster.sync();        // peers may still be reading this CTA's partial tile
+#pragma unroll
+        for (int i = 0; i < MAX_ROWS; ++i) {
+            const float t = warp_sum(sq[i]);
+            if (lane == 0) red[warp * MB + i] = t;
+        }
+        __syncthreads();
+        if (threadIdx.x < MAX_ROWS) {
+            const int m = rank + threadIdx.x * csize;
+            if (m < m_valid)
+                p.ss_out[(int64_t)blockIdx.x * p.M + m0 + m] = red[threadIdx.x] + red[MB + threadIdx.x] +
+                                                              red[2 * MB + threadIdx.x] + red[3 * MB + threadIdx.x];
+        }
     }
+    if (splits > 1) cg::this_cluster().sync();     // peers may still be reading this CTA's tile
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -298,7 +361,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
     const size_t ring = (size_t)STAGES * STAGE_BYTES;
     const size_t part = (size_t)MB * TC_BM * sizeof(float);
-    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 + 5 * MB * sizeof(float) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MB, STAGES>,
@@ -330,12 +393,21 @@ extern "C" int acorn_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int64_t 
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && M <= (1 << 30);
 }
 
-extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
-                             int N, int K, int out_f32, int splits, cudaStream_t stream) {
+// mode, ss_in .. ss_out: see TcParams.  Modes other than plain, and ss_in, are for at most 32 rows.
+extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
+                                int N, int K, int out_f32, int splits, int mode, const float* ss_in, int ss_parts,
+                                int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
+                                float* ss_out, cudaStream_t stream) {
     if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
+    if (mode != TC_MODE_PLAIN && (M > 32 || out_f32)) return ACORN_ERR_UNSUPPORTED;
+    if (mode == TC_MODE_SWIGLU && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
+    if (mode == TC_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
+    if (ss_in != nullptr && (M > 32 || ss_parts < 1 || norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
     TcParams p;
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.kblocks = (K + TC_BK - 1) / TC_BK; p.out_f32 = out_f32;
+    p.mode = mode; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_width = norm_width; p.eps = eps;
+    p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.ss_out = ss_out;
     if (splits > p.kblocks) splits = p.kblocks;
     const int mb = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     CUtensorMap mw, mx;
@@ -349,6 +421,12 @@ extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t 
         case 64: return launch_tc<64, 4>(mw, mx, p, splits, stream);
         default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
     }
+}
+
+extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
+                             int N, int K, int out_f32, int splits, cudaStream_t stream) {
+    return acorn_gemm_tc_ex(x, ldx, w, ldw, out, ldo, M, N, K, out_f32, splits, TC_MODE_PLAIN, nullptr, 0, 0, 0.f,
+                            nullptr, 0, nullptr, nullptr, stream);
 }
 
 // Reads and clears the flag that a bounded wait sets when it gives up (0 = no error).

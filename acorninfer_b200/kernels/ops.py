@@ -9,6 +9,7 @@ to fall back to.  Tensors are passed as raw device pointers.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -45,7 +46,7 @@ def lib():
 class _Sigs:
     acorn_embed = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     acorn_add_rmsnorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
-    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_cast = [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
     acorn_qk_rope_kv = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
@@ -63,6 +64,8 @@ class _Sigs:
     acorn_attention_prefill_supported = [c_int, c_int, c_int]
     acorn_gemm_tc = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                      c_void_p]
+    acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                        c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
     acorn_gemm_tc_error = []
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
@@ -157,16 +160,20 @@ def add_rmsnorm(resid32: torch.Tensor, delta: torch.Tensor | None, weight32: tor
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int | None = None) -> torch.Tensor:
+    """silu(gate) * up.  A row holds, per block of ``block`` outputs, the gate values then the up
+    values; the default (block = I) is the plain layout ``[gate | up]``."""
     _check(gate_up, "gate_up", None, 2)
     T, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError("gate_up must have an even width")
+    block = block or two_i // 2
+    if (two_i // 2) % block:
+        raise KernelError(f"swiglu: block {block} does not divide the width {two_i // 2}")
     if out is None:
         out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(out, "out", gate_up.dtype, 2)
-    _ok(lib().acorn_swiglu(gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, dtype_code(gate_up.dtype),
+    _ok(lib().acorn_swiglu(gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, block, dtype_code(gate_up.dtype),
                            _stream()), "swiglu")
     return out
 
@@ -360,23 +367,74 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
 GEMM_TC_MAX_ROWS = 32
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
-            out: torch.Tensor | None = None) -> torch.Tensor:
-    """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate)."""
-    if not gemm_tc_supported(x, w):
-        raise KernelError(f"gemm_tc does not take x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
+@dataclass
+class NormedRows:
+    """Activations whose rows still lack their RMS factor: ``x = residual * norm weight`` and, per
+    row, partial sums of ``residual^2`` (``ss`` [parts, rows]).  The matrix product that consumes
+    them multiplies each output row by ``rsqrt(sum(ss) / width + eps)``: the norm costs no kernel."""
+
+    x: torch.Tensor
+    ss: torch.Tensor
+    eps: float
+    width: int
+
+
+@dataclass
+class AddNormEpilogue:
+    """What the last product of a part does with its result instead of writing it: add it to the
+    float32 residual stream (in place) and hand on ``NormedRows`` for the norm with this weight."""
+
+    resid32: torch.Tensor
+    weight32: torch.Tensor
+    eps: float
+
+
+def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
+            out: torch.Tensor | None = None, epilogue: AddNormEpilogue | None = None, swiglu: bool = False):
+    """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate).
+
+    ``x`` may be ``NormedRows`` (at most 32 rows): the rows' RMS factors are applied to the product.
+    ``epilogue``: see ``AddNormEpilogue`` (returns ``NormedRows``).  ``swiglu``: ``w`` holds blocks
+    of 64 gate rows and 64 up rows; returns ``silu(gate) * up`` [M, N / 2]."""
+    rows = x if isinstance(x, NormedRows) else None
+    xt = rows.x if rows is not None else x
+    if not gemm_tc_supported(xt, w):
+        raise KernelError(f"gemm_tc does not take x {tuple(xt.shape)} {xt.dtype} stride {xt.stride()}, "
                           f"w {tuple(w.shape)} {w.dtype}: bf16, K contiguous, K and strides multiples of 8")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_tc writes bfloat16 or float32")
-    M, K = x.shape
+    M, K = xt.shape
     N = w.shape[0]
+    if (rows is not None or epilogue is not None or swiglu) and M > 32:
+        raise KernelError(f"gemm_tc: fused norm / SwiGLU epilogues take at most 32 rows, got {M}")
     if splits is None:
         splits = gemm_tc_splits(M, N, K)
+    mode, resid, ldr, norm_w, ss_out = 0, None, 0, None, None
+    out_cols = N
+    if epilogue is not None:
+        if swiglu or out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc: the add-norm epilogue writes bfloat16 and excludes SwiGLU")
+        _check(epilogue.resid32, "resid32", torch.float32, 2)
+        _check(epilogue.weight32, "norm weight", torch.float32, 1)
+        if epilogue.resid32.shape != (M, N) or epilogue.weight32.numel() != N:
+            raise KernelError("gemm_tc: residual / norm weight do not match the product's shape")
+        mode, resid, ldr, norm_w = 1, epilogue.resid32, epilogue.resid32.stride(0), epilogue.weight32
+        ss_out = torch.empty((-(-N // 128), M), dtype=torch.float32, device=xt.device)
+    elif swiglu:
+        if N % 128 or out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc: SwiGLU epilogue needs N a multiple of 128 and bfloat16 output")
+        mode, out_cols = 2, N // 2
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, out_cols), dtype=out_dtype, device=xt.device)
     _check(out, "out", out_dtype, 2)
-    _ok(lib().acorn_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-                            M, N, K, 1 if out_dtype == torch.float32 else 0, int(splits), _stream()), "gemm_tc")
+    _ok(lib().acorn_gemm_tc_ex(
+        xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+        1 if out_dtype == torch.float32 else 0, int(splits), mode,
+        rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
+        rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
+        _ptr(resid), ldr, _ptr(norm_w), _ptr(ss_out), _stream()), "gemm_tc")
+    if epilogue is not None:
+        return NormedRows(out, ss_out, epilogue.eps, N)
     return out
 
 
@@ -385,7 +443,13 @@ def gemm_tc_error() -> int:
     return int(lib().acorn_gemm_tc_error())
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def fused_rows_ok(num_rows: int, dtype: torch.dtype) -> bool:
+    """Whether products of this many rows run on the tcgen05 kernel with fused norm epilogues."""
+    return dtype == torch.bfloat16 and 0 < num_rows <= GEMM_TC_MAX_ROWS
+
+
+def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: AddNormEpilogue | None = None,
+           swiglu: bool = False):
     """x [T, K] times w [N, K] transposed.
 
     float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
@@ -393,8 +457,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     that the library matrix product (cuBLAS); float32 accumulation either way, and
     ``out_dtype=float32`` keeps the accumulator's precision (used for logits).
     A weight stored in float32 under a bfloat16 engine is multiplied in float32.
+    ``x`` as ``NormedRows``, ``epilogue`` and ``swiglu`` exist on the tcgen05 path only
+    (``fused_rows_ok``); asking for them elsewhere is an error, not a silent detour.
     """
-    out_dtype = out_dtype or x.dtype
+    fused = isinstance(x, NormedRows) or epilogue is not None or swiglu
+    xt = x.x if isinstance(x, NormedRows) else x
+    out_dtype = out_dtype or xt.dtype
+    if fused:
+        if not (fused_rows_ok(xt.shape[0], xt.dtype) and gemm_tc_supported(xt, w)):
+            raise KernelError(f"linear: fused epilogues need the tcgen05 path (bf16, <= {GEMM_TC_MAX_ROWS} rows, "
+                              f"K a multiple of 8); got {tuple(xt.shape)} {xt.dtype} x {tuple(w.shape)} {w.dtype}")
+        return gemm_tc(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
     if w.dtype == torch.float32:
         y = gemm_f32(cast(x, torch.float32) if x.dtype != torch.float32 else x, w)
         return y if out_dtype == torch.float32 else cast(y, out_dtype)

@@ -134,8 +134,12 @@ class Decoder:
         """Runs the step's tokens; returns float32 logits [wanted, vocab] (None if none wanted)."""
         resid32 = ops.embed(inputs.token_ids, self.embedding)
         delta = None
-        for i, e in enumerate(self.spec.schedule):
-            resid32, delta = self.blocks[e.layer].forward(resid32, delta, inputs, caches[i])
+        sched = self.spec.schedule
+        for i, e in enumerate(sched):
+            # the norm that consumes this run's output: the next run's first norm (the final norm
+            # works on selected rows only and keeps its own kernel)
+            nxt = self.blocks[sched[i + 1].layer].first_norm(inputs.num_tokens) if i + 1 < len(sched) else None
+            resid32, delta = self.blocks[e.layer].forward(resid32, delta, inputs, caches[i], next_norm=nxt)
         if inputs.num_logits == 0:
             return None
         h = self.final_norm.add_forward(resid32, delta, rows=inputs.logit_tokens)

@@ -25,6 +25,7 @@ from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, TensorSpec
 @MIXERS.register("attention")
 class Attention(Mixer):
     graph_safe = True
+    supports_epilogue = True
 
     def __init__(self, ctx: BuildContext, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: str | None, scale: float, qk_norm_eps: float | None = None,
@@ -68,7 +69,11 @@ class Attention(Mixer):
     def cache_needs(self):
         return CacheNeeds(kv=KVNeeds(self.nkv, self.d, self.window))
 
-    def forward(self, x, inputs, cache):
+    def fusable(self, num_rows):
+        return (ops.fused_rows_ok(num_rows, self.ctx.dtype) and self.w_qkv.dtype == torch.bfloat16
+                and self.w_o.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and (self.nq * self.d) % 8 == 0)
+
+    def forward(self, x, inputs, cache, epilogue=None):
         g = inputs.groups[cache.group]
         qkv = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
         pos = self.position
@@ -79,7 +84,7 @@ class Attention(Mixer):
                        pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
                        self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write)
         out = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window)
-        return ops.linear(out, self.w_o, out_dtype=self.ctx.dtype)
+        return ops.linear(out, self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue)
 
 
 _NO_FREQ: dict = {}

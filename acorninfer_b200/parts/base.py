@@ -150,6 +150,12 @@ class Norm(Part):
     def forward(self, x32: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def as_epilogue(self, resid32: torch.Tensor):
+        """An epilogue object with which the matrix product before this norm adds its result to
+        the residual stream and hands on rows that only lack their RMS factor, or None if this
+        norm cannot be fused that way."""
+        return None
+
     def add_forward(self, resid32: torch.Tensor, delta: torch.Tensor | None,
                     out: torch.Tensor | None = None) -> torch.Tensor:
         """resid32 += delta (in place, float32), then the norm of it."""
@@ -161,14 +167,26 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True: ``forward`` takes ``x`` as ``NormedRows`` and an ``epilogue`` for its last product
+    # (see ``kernels.ops.NormedRows`` / ``AddNormEpilogue``) when ``fusable(rows)`` says so.
+    supports_epilogue = False
+
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds()
+
+    def fusable(self, num_rows: int) -> bool:
+        return False
 
     def forward(self, x: torch.Tensor, inputs: "Any", cache: "Any") -> torch.Tensor:
         raise NotImplementedError
 
 
 class FeedForward(Part):
+    supports_epilogue = False
+
+    def fusable(self, num_rows: int) -> bool:
+        return False
+
     def forward(self, x: torch.Tensor, inputs: "Any") -> torch.Tensor:
         raise NotImplementedError
 
@@ -181,9 +199,19 @@ class Block(Part):
         self.feed_forward = feed_forward
         self.norms = norms
 
-    def forward(self, resid32: torch.Tensor, delta: torch.Tensor | None, inputs: "Any",
-                cache: "Any") -> tuple[torch.Tensor, torch.Tensor]:
+    def forward(self, resid32: torch.Tensor, delta, inputs: "Any", cache: "Any",
+                next_norm: "Norm | None" = None) -> tuple[torch.Tensor, Any]:
+        """``delta`` is what the previous block still has to add to the residual stream, or
+        ``NormedRows`` if that block already added it and prepared this block's first norm.
+        ``next_norm``: the norm that will consume this block's output (the next block's first
+        norm), offered so that the sum and that norm can be fused into this block's last product."""
         raise NotImplementedError
+
+    def first_norm(self, num_rows: int) -> "Norm | None":
+        """The norm this block applies first to the residual stream, if for a step of ``num_rows``
+        tokens the block accepts it already applied up to the RMS factor (``NormedRows``);
+        None otherwise."""
+        return None
 
 
 # --------------------------------------------------------------------------- registries

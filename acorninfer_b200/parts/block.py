@@ -8,6 +8,7 @@ where ``delta`` is what the previous block still has to add, and returns the sam
 
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import BLOCKS, Block
 
 
@@ -21,9 +22,24 @@ class PreNormBlock(Block):
         if missing:
             raise ValueError(f"prenorm block needs norms named 'mixer' and 'feed_forward'; missing {sorted(missing)}")
 
-    def forward(self, resid32, delta, inputs, cache):
-        h = self.norms["mixer"].add_forward(resid32, delta)
-        delta = self.mixer.forward(h, inputs, cache)
-        h = self.norms["feed_forward"].add_forward(resid32, delta)
-        delta = self.feed_forward.forward(h, inputs)
-        return resid32, delta
+    def _fuses(self, num_rows):
+        return (self.mixer.supports_epilogue and self.feed_forward.supports_epilogue
+                and self.mixer.fusable(num_rows) and self.feed_forward.fusable(num_rows))
+
+    def first_norm(self, num_rows):
+        return self.norms["mixer"] if self._fuses(num_rows) else None
+
+    def forward(self, resid32, delta, inputs, cache, next_norm=None):
+        # With few rows on the tensor-core path, each residual sum and the norm after it are done
+        # by the product before them (no kernel of their own); otherwise by the fused norm kernel.
+        fuse = self._fuses(inputs.num_tokens)
+        h = delta if isinstance(delta, ops.NormedRows) else self.norms["mixer"].add_forward(resid32, delta)
+        ep = self.norms["feed_forward"].as_epilogue(resid32) if fuse else None
+        if ep is not None:
+            h = self.mixer.forward(h, inputs, cache, epilogue=ep)
+        else:
+            h = self.norms["feed_forward"].add_forward(resid32, self.mixer.forward(h, inputs, cache))
+        ep = next_norm.as_epilogue(resid32) if (fuse and next_norm is not None) else None
+        if ep is not None:
+            return resid32, self.feed_forward.forward(h, inputs, epilogue=ep)
+        return resid32, self.feed_forward.forward(h, inputs)

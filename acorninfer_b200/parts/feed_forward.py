@@ -14,12 +14,17 @@ from .base import FEED_FORWARDS, BuildContext, FeedForward, TensorSpec
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
     graph_safe = True
+    supports_epilogue = True
 
     def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int):
         self.ctx = ctx
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.w_gate_up = self.w_down = None
+        # gate and up rows are stored in blocks: `block` gate rows, then the `block` up rows of the
+        # same outputs.  64 puts a gate/up pair of blocks in every 128-row tile of the tcgen05
+        # product, whose epilogue can then apply SwiGLU itself.
+        self.block = 64 if intermediate_size % 64 == 0 else intermediate_size
 
     def tensor_specs(self):
         return {
@@ -31,10 +36,21 @@ class SwiGLU(FeedForward):
     def bind(self, tensors):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         dtype = g.dtype if g.dtype == u.dtype else torch.float32
-        self.w_gate_up = torch.cat([g.to(dtype), u.to(dtype)], dim=0).contiguous()
+        b, I, H = self.block, self.intermediate_size, self.hidden_size
+        self.w_gate_up = torch.stack([g.to(dtype).view(I // b, b, H), u.to(dtype).view(I // b, b, H)], dim=1) \
+            .reshape(2 * I, H).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
-    def forward(self, x, inputs):
-        gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
-        h = ops.swiglu(gu)
-        return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype)
+    def fusable(self, num_rows):
+        return (ops.fused_rows_ok(num_rows, self.ctx.dtype) and self.w_gate_up.dtype == torch.bfloat16
+                and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+                and self.intermediate_size % 8 == 0)
+
+    def forward(self, x, inputs, epilogue=None):
+        rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
+        if self.block == 64 and self.fusable(rows):
+            h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True)
+        else:
+            gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
+            h = ops.swiglu(gu, block=self.block)
+        return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, epilogue=epilogue)

@@ -31,6 +31,9 @@ class RMSNorm(Norm):
         # Norm weights are held in float32 whatever they were stored as (widening is exact).
         self.weight32 = tensors["weight"].to(torch.float32).contiguous()
 
+    def as_epilogue(self, resid32):
+        return ops.AddNormEpilogue(resid32, self.weight32, self.eps)
+
     def forward(self, x32, out=None, rows=None):
         return ops.add_rmsnorm(x32, None, self.weight32, self.eps, self.ctx.dtype, row_idx=rows, out=out)
 

@@ -42,3 +42,49 @@ def test_gemm_tc_strided_operands_and_refusals():
         ops().gemm_tc(torch.zeros(4, 36, device=DEV, dtype=torch.bfloat16), torch.zeros(8, 36, device=DEV, dtype=torch.bfloat16))
     with pytest.raises(KernelError):
         ops().gemm_tc(torch.zeros(4, 64, device=DEV), torch.zeros(8, 64, device=DEV))
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(1, 256, 128, 1), (8, 4096, 512, 8), (13, 200, 264, 2), (32, 384, 1024, 4)])
+def test_gemm_tc_add_norm_epilogue_and_normed_rows(M, N, K, splits):
+    """product -> residual += ; h = residual * w_norm (no RMS factor yet) + partial sums of squares;
+    the next product applies rsqrt(mean + eps) to its rows: together they equal add + RMSNorm + product."""
+    from acorninfer_b200.kernels.ops import AddNormEpilogue, NormedRows
+    torch.manual_seed(N + M)
+    eps = 1e-5
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w1 = (torch.randn(N, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    resid = torch.randn(M, N, device=DEV)
+    nw = 1 + 0.1 * torch.randn(N, device=DEV)
+    N2 = 136
+    w2 = (torch.randn(N2, N, device=DEV) / N ** 0.5).to(torch.bfloat16)
+    want_resid = resid.double() + x.double() @ w1.double().T
+    want_h = want_resid * torch.rsqrt(want_resid.pow(2).mean(-1, keepdim=True) + eps) * nw.double()
+    want_out = want_h @ w2.double().T
+    r = resid.clone()
+    rows = ops().gemm_tc(x, w1, torch.bfloat16, splits=splits, epilogue=AddNormEpilogue(r, nw, eps))
+    assert isinstance(rows, NormedRows) and rows.ss.shape == (-(-N // 128), M)
+    assert torch.allclose(r.double(), want_resid, atol=2e-3, rtol=1e-4)
+    assert torch.allclose(rows.ss.sum(0).double(), want_resid.pow(2).sum(-1), rtol=1e-3)
+    if N % 8 == 0:
+        out = ops().gemm_tc(rows, w2, torch.float32, splits=1)
+        assert torch.allclose(out.double(), want_out, atol=3e-2, rtol=3e-2)
+        out2 = ops().gemm_tc(rows, w2, torch.float32, splits=2)
+        assert torch.allclose(out2.double(), want_out, atol=3e-2, rtol=3e-2)
+    assert ops().gemm_tc_error() == 0
+
+
+@pytest.mark.parametrize("M,I,K,splits", [(1, 64, 64, 1), (8, 640, 512, 1), (20, 192, 1024, 4)])
+def test_gemm_tc_swiglu_epilogue(M, I, K, splits):
+    torch.manual_seed(I)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    g = (torch.randn(I, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    u = (torch.randn(I, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    w = torch.stack([g.view(I // 64, 64, K), u.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+    out = ops().gemm_tc(x, w, torch.bfloat16, splits=splits, swiglu=True)
+    gg, uu = x.double() @ g.double().T, x.double() @ u.double().T
+    assert out.shape == (M, I)
+    assert torch.allclose(out.double(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=2e-2)
+    # the stand-alone kernel reads the same block layout
+    gu = ops().gemm_tc(x, w, torch.bfloat16, splits=1)
+    assert torch.allclose(ops().swiglu(gu, block=64).float(), out.float(), atol=2e-2, rtol=2e-2)
+    assert ops().gemm_tc_error() == 0
