@@ -59,27 +59,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid32, const T* __restr
 // passes: for widths that are a multiple of 4 and at most threads * 4 * RMS_MAX_ITER.
 #define RMS_MAX_ITER 8
 
-template <typename T> struct Vec4;
-template <> struct Vec4<float> {
-    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
-    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-};
-template <> struct Vec4<bf16> {
-    static __device__ __forceinline__ float4 load(const bf16* p) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(p);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-        return make_float4(a.x, a.y, b.x, b.y);
-    }
-    static __device__ __forceinline__ void store(bf16* p, float4 v) {
-        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-        uint2 raw;
-        raw.x = *reinterpret_cast<uint32_t*>(&a);
-        raw.y = *reinterpret_cast<uint32_t*>(&b);
-        *reinterpret_cast<uint2*>(p) = raw;
-    }
-};
-
 template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid32, const T* __restrict__ delta,
                                        const float* __restrict__ w, T* __restrict__ out,

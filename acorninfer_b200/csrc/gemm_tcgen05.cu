@@ -217,8 +217,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     // tiles of the cluster's CTAs are then summed in rank order, each CTA finishing the rows
     // m = rank, rank + csize, ...; without a split the CTA finishes all rows of its own tile.
     float* part = reinterpret_cast<float*>(smem);
-    float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // [4 warps][MB] + inv[MB]
-    float* inv_s = red + 4 * MB;
+    constexpr int RED_FLOATS = 4 * MB > TC_THREADS ? 4 * MB : TC_THREADS;
+    float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // reduction scratch, then inv[MB]
+    float* inv_s = red + RED_FLOATS;
 #pragma unroll
     for (int c = 0; c < MB; c += 16) {
         float v[16];
@@ -233,14 +234,23 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     }
     // Rows of x that arrive un-normalised (x = residual * norm weight): the factor
     // rsqrt(mean(residual^2) + eps) of each row is applied to the product here.
-    if (threadIdx.x < MB) {
-        float f = 1.f;
-        if (p.ss_in != nullptr && m0 + (int)threadIdx.x < p.M) {
-            float ss = 0.f;
-            for (int q = 0; q < p.ss_parts; ++q) ss += p.ss_in[(int64_t)q * p.M + m0 + threadIdx.x];
-            f = rsqrtf(ss / (float)p.norm_width + p.eps);
+    if (p.ss_in != nullptr) {
+        // 128 threads: row = t % MB, the partial sums of a row are shared out over 128 / MB threads
+        constexpr int G = TC_THREADS / MB;
+        const int m = threadIdx.x % MB, g = threadIdx.x / MB;
+        float ss = 0.f;
+        if (g < G && m0 + m < p.M)
+            for (int q = g; q < p.ss_parts; q += G) ss += p.ss_in[(int64_t)q * p.M + m0 + m];
+        if (g < G) red[g * MB + m] = ss;
+        __syncthreads();
+        if (threadIdx.x < MB) {
+            float tot = 0.f;
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) tot += red[gg * MB + threadIdx.x];
+            inv_s[threadIdx.x] = rsqrtf(tot / (float)p.norm_width + p.eps);
         }
-        inv_s[threadIdx.x] = f;
+    } else if (threadIdx.x < MB) {
+        inv_s[threadIdx.x] = 1.f;
     }
     int rank = 0, csize = 1;
     if (splits > 1) {
@@ -361,7 +371,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
     const size_t ring = (size_t)STAGES * STAGE_BYTES;
     const size_t part = (size_t)MB * TC_BM * sizeof(float);
-    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 + 5 * MB * sizeof(float) + 1024;
+    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 + ((4 * MB > TC_THREADS ? 4 * MB : TC_THREADS) + MB) * sizeof(float) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MB, STAGES>,

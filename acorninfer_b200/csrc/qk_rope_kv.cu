@@ -75,6 +75,79 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
     for (int i = rot + lane; i < d; i += 32) dst[i] = from_float<T>(x[i]);
 }
 
+// The same for the common case (whole head rotated, half pairing, head size 16, 32, 64, 128 or
+// 256): a group of d / 8 lanes per (token, head), each lane holding four rotary pairs
+// (x[4l .. 4l+3], x[d/2 + 4l .. d/2 + 4l+3]) in registers; vector loads and stores, no shared memory.
+template <typename T, int G>
+__global__ void qk_rope_kv_vec_kernel(T* __restrict__ qkv, const float* __restrict__ q_w,
+                                      const float* __restrict__ k_w, const float* __restrict__ inv_freq,
+                                      const int* __restrict__ positions, const int* __restrict__ token_row,
+                                      const int* __restrict__ block_table, const int* __restrict__ page_base,
+                                      int table_stride, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                      int tokens, int nq, int nkv, int P, float eps, int write_kv) {
+    constexpr int D = G * 8, HALF = D / 2;
+    pdl_wait();
+    pdl_trigger();
+    const int heads = write_kv ? (nq + 2 * nkv) : nq;
+    const int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const int l = threadIdx.x % G;
+    const bool active = item < (int64_t)tokens * heads;
+    const int64_t it = active ? item : 0;
+    const int t = (int)(it / heads);
+    const int h = (int)(it - (int64_t)t * heads);
+    T* src = qkv + ((int64_t)t * (nq + 2 * nkv) + h) * D;
+    const int pos = positions[t];
+    T* dst = src;
+    if (h >= nq) {
+        const int r = token_row[t];
+        const int kvh = (h - nq) % nkv;
+        const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
+        T* base = (h < nq + nkv) ? k_pages : v_pages;
+        dst = base + (((int64_t)page * nkv + kvh) * P + (pos % P)) * D;
+    }
+    float4 a = Vec4<T>::load(src + 4 * l), b = Vec4<T>::load(src + HALF + 4 * l);
+    if (h < nq + nkv) {
+        const float* w = (h < nq) ? q_w : k_w;
+        if (w) {
+            float ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = rsqrtf(ss / (float)D + eps);
+            const float4 wa = *reinterpret_cast<const float4*>(w + 4 * l);
+            const float4 wb = *reinterpret_cast<const float4*>(w + HALF + 4 * l);
+            a = make_float4(a.x * inv * wa.x, a.y * inv * wa.y, a.z * inv * wa.z, a.w * inv * wa.w);
+            b = make_float4(b.x * inv * wb.x, b.y * inv * wb.y, b.z * inv * wb.z, b.w * inv * wb.w);
+        }
+        const float4 f = *reinterpret_cast<const float4*>(inv_freq + 4 * l);
+        float s0, c0, s1, c1, s2, c2, s3, c3;
+        sincosf((float)pos * f.x, &s0, &c0);
+        sincosf((float)pos * f.y, &s1, &c1);
+        sincosf((float)pos * f.z, &s2, &c2);
+        sincosf((float)pos * f.w, &s3, &c3);
+        const float4 ra = make_float4(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1, a.z * c2 - b.z * s2, a.w * c3 - b.w * s3);
+        const float4 rb = make_float4(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1, b.z * c2 + a.z * s2, b.w * c3 + a.w * s3);
+        a = ra;
+        b = rb;
+    }
+    if (active) {
+        Vec4<T>::store(dst + 4 * l, a);
+        Vec4<T>::store(dst + HALF + 4 * l, b);
+    }
+}
+
+template <typename T, int G>
+static int launch_rope_vec(T* qkv, const float* q_w, const float* k_w, const float* inv_freq, const int* positions,
+                           const int* token_row, const int* block_table, const int* page_base, int table_stride,
+                           T* k_pages, T* v_pages, int tokens, int nq, int nkv, int P, float eps, int write_kv,
+                           cudaStream_t stream) {
+    const int heads = write_kv ? (nq + 2 * nkv) : nq;
+    const int64_t threads = (int64_t)tokens * heads * G;
+    const int64_t blocks = (threads + 255) / 256;
+    return acorn_launch(qk_rope_kv_vec_kernel<T, G>, dim3((unsigned)blocks), dim3(256), 0, stream, qkv, q_w, k_w,
+                        inv_freq, positions, token_row, block_table, page_base, table_stride, k_pages, v_pages, tokens,
+                        nq, nkv, P, eps, write_kv);
+}
+
 extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, const float* inv_freq,
                                 const int* positions, const int* token_row, const int* block_table,
                                 const int* page_base, int table_stride, void* k_pages, void* v_pages,
@@ -82,6 +155,21 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
                                 float eps, int write_kv, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d > 1024 || rot > d || (rot & 1)) return ACORN_ERR_UNSUPPORTED;
+    if (rot == d && pairing == 0 && (d == 16 || d == 32 || d == 64 || d == 128 || d == 256)) {
+#define ROPE_VEC(G)                                                                                                  \
+    ACORN_DISPATCH_DTYPE(dtype, T, return (launch_rope_vec<T, G>((T*)qkv, q_w, k_w, inv_freq, positions, token_row,   \
+                                                                  block_table, page_base, table_stride, (T*)k_pages,   \
+                                                                  (T*)v_pages, tokens, nq, nkv, P, eps, write_kv,      \
+                                                                  stream)))
+        switch (d) {
+            case 16: ROPE_VEC(2); break;
+            case 32: ROPE_VEC(4); break;
+            case 64: ROPE_VEC(8); break;
+            case 128: ROPE_VEC(16); break;
+            default: ROPE_VEC(32); break;
+        }
+#undef ROPE_VEC
+    }
     const int warps = 4;
     const int heads = write_kv ? (nq + 2 * nkv) : nq;
     const int64_t items = (int64_t)tokens * heads;

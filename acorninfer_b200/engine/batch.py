@@ -59,6 +59,8 @@ class StepPlan:
     max_q_len: int
     all_decode: bool            # every row is a single token
     q_tiles: np.ndarray = None  # [n_tiles, 2]: (row, first token within the row) of each 64-token query tile
+                                # of the rows that bring more than one token
+    single_tokens: np.ndarray = None   # flat indices of the tokens of single-token rows (decoded tokens)
 
     @property
     def num_logits(self) -> int:
@@ -141,10 +143,14 @@ def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
             kv_len[r] = new_len
             base[r] = e.cache.page_base[g.index]
         groups.append(GroupPlan(kv_len, base, bt, int(kv_len.max()) if R else 0))
-    tiles = [(r, q0) for r, n in enumerate(lens) for q0 in range(0, n, Q_TILE)]
+    # Rows of one token go to the decode attention kernel, longer rows to the prefill kernel in
+    # tiles of Q_TILE queries.  When a kernel does not take the model's head size, the caller
+    # falls back to the plain kernel for all tokens.
+    tiles = [(r, q0) for r, n in enumerate(lens) if n > 1 for q0 in range(0, n, Q_TILE)]
+    singles = [int(row_start[r]) for r, n in enumerate(lens) if n == 1]
     return StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
                     np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens),
-                    np.asarray(tiles, np.int32).reshape(-1, 2))
+                    np.asarray(tiles, np.int32).reshape(-1, 2), np.asarray(singles, np.int32))
 
 
 # --------------------------------------------------------------------------- device side
@@ -174,6 +180,7 @@ class StepInputs:
     groups: list[GroupInputs]
     plan: StepPlan
     q_tiles: object = None
+    single_tokens: object = None
     scratch: dict = field(default_factory=dict)     # per-step products shared by parts (e.g. split plans)
 
     @property
@@ -219,6 +226,7 @@ class StepWorkspace:
         put("row_slot", R)
         put("logit_tokens", plan.num_logits)
         put("q_tiles", plan.q_tiles.size)
+        put("single_tokens", plan.single_tokens.size)
         for i, g in enumerate(plan.groups):
             put(f"g{i}.kv_len", R)
             put(f"g{i}.page_base", R)
@@ -239,6 +247,7 @@ class StepWorkspace:
             "token_ids": plan.token_ids, "positions": plan.positions, "token_row": plan.token_row,
             "row_start": plan.row_start, "row_pos": plan.row_pos, "row_slot": plan.row_slot,
             "logit_tokens": plan.logit_tokens, "q_tiles": plan.q_tiles.reshape(-1),
+            "single_tokens": plan.single_tokens,
         }
         for gi, g in enumerate(plan.groups):
             arrays[f"g{gi}.kv_len"] = g.kv_len
@@ -262,4 +271,4 @@ class StepWorkspace:
             groups.append(GroupInputs(view(f"g{gi}.kv_len"), view(f"g{gi}.page_base"), bt, g.max_kv_len))
         return StepInputs(plan.num_tokens, plan.num_rows, view("token_ids"), view("positions"), view("token_row"),
                           view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan,
-                          view("q_tiles").view(-1, 2))
+                          view("q_tiles").view(-1, 2), view("single_tokens"))

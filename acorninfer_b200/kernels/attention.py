@@ -39,10 +39,25 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             return ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                         group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
                                         nq, nkv, d, scale, window, splits)
-        if ops.attention_prefill_supported(nq, nkv, d):
-            return ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
-                                         group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles,
-                                         inputs.num_tokens, nq, nkv, d, scale, window)
+        n_single = int(inputs.plan.single_tokens.size)
+        if ops.attention_prefill_supported(nq, nkv, d) and (n_single == 0 or (
+                ops.attention_decode_supported(nq, nkv, d) and n_single <= 65535)):
+            # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
+            # decode kernel, both writing their rows of one output
+            out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
+            if inputs.q_tiles.shape[0]:
+                ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
+                                      group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles,
+                                      inputs.num_tokens, nq, nkv, d, scale, window, out=out)
+            if n_single:
+                bound = group.block_table.shape[1] * P
+                if window:
+                    bound = min(bound, window)
+                ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
+                                     group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
+                                     nq, nkv, d, scale, window, decode_splits(n_single, nkv, bound),
+                                     token_list=inputs.single_tokens, out=out)
+            return out
     return ops.attention_plain(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
                                nq, nkv, d, scale, window)

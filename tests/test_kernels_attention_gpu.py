@@ -35,7 +35,8 @@ def rope_reference(x, positions, rot, theta, interleaved):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,d,rot,inter,norm,P", [
     (4, 2, 16, 16, False, True, 4), (10, 2, 48, 48, False, True, 16), (3, 3, 80, 32, True, True, 8),
-    (6, 1, 112, 112, False, False, 32), (2, 1, 272, 64, False, True, 16)])
+    (6, 1, 112, 112, False, False, 32), (2, 1, 272, 64, False, True, 16), (32, 8, 128, 128, False, True, 16),
+    (5, 5, 64, 64, False, False, 8), (8, 1, 32, 32, False, True, 4), (2, 2, 256, 256, False, True, 16)])
 def test_qk_rope_kv(dtype, nq, nkv, d, rot, inter, norm, P):
     theta, eps, NP = 5e5, 2e-6, 1400
     lay = rows_layout([0, 37, 4095, 15], [21, 1, 2, 17], P, NP, seed=1)
