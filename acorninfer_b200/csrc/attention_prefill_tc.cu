@@ -1,0 +1,304 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05), head size 128, bfloat16:
+// causal attention of a tile of 128 consecutive queries of one request against its keys and
+// values in the paged cache, S = Q K^T and P V computed by tcgen05.mma with the accumulators
+// in tensor memory, K/V/Q tiles brought by TMA through the block table.
+//
+// One CTA per (tile of 128 queries, query head), 6 warps:
+//   warps 0-3  softmax: thread r owns query row r (= TMEM lane r): reads its row of S with
+//              tcgen05.ld, masks by absolute position (causal, window), online softmax in
+//              float32 base 2, writes P (bfloat16) into a swizzled shared-memory tile, then adds
+//              the block's P V (read from TMEM) into its 128 float32 output accumulators.
+//   warp 4     producer: TMA loads of Q (once) and, per block of 64 keys, of the K and V page
+//              tiles ((page, kv head) tiles are contiguous [page_size x 128] in the cache).
+//   warp 5     MMA issuer: S[j] = Q K_j^T into one of two S buffers (so the next block's scores
+//              are computed while the softmax warps work on this one), O_j = P_j V_j.
+// Tensor memory: S0, S1 (64 columns each), O (128 columns).  V is the MN-major B operand of the
+// second product (head dims contiguous); P is a K-major A operand written by the softmax
+// warps (generic proxy) and fenced to the async proxy.
+//
+// Every mbarrier wait is bounded; a wait that gives up records g_attn_tc_error and the CTA
+// drains without touching tensor memory it does not own.
+#include "tcgen05_helpers.cuh"
+
+#define ATC_D 128
+#define ATC_BM 128
+#define ATC_BN 64
+#define ATC_STAGES 3
+#define ATC_THREADS 192
+
+__device__ int g_attn_tc_error = 0;
+
+struct AttnTcParams {
+    bf16* out;               // [tokens, nq * 128]
+    const int* block_table;
+    const int* page_base;
+    const int* row_start;
+    const int* row_pos;
+    const int* tiles;        // [n_tiles, 2]: row, first token of the tile within the row
+    int table_stride, nq, nkv, logP, window;
+    float scale_log2;
+};
+
+// shared memory map (bytes, all tile regions 1024-aligned)
+#define ATC_Q_BYTES (2 * ATC_BM * 128)                    // two 64-element halves of [128 x 128]
+#define ATC_KV_HALF (ATC_BN * 128)                         // one half of a K or V block: [64 keys x 64 dims]
+#define ATC_STAGE_BYTES (4 * ATC_KV_HALF)                  // K half 0, K half 1, V half 0, V half 1
+#define ATC_P_BYTES (ATC_BM * 128)                         // [128 rows x 64 keys] bf16
+#define ATC_SMEM_TILES (ATC_Q_BYTES + ATC_STAGES * ATC_STAGE_BYTES + 2 * ATC_P_BYTES)
+
+__global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                              const __grid_constant__ CUtensorMap map_k,
+                                                                              const __grid_constant__ CUtensorMap map_v,
+                                                                              const AttnTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sQ = smem;
+    uint8_t* sKV = sQ + ATC_Q_BYTES;
+    uint8_t* sP = sKV + ATC_STAGES * ATC_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATC_P_BYTES);
+    // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full, o_free
+    const uint32_t q_full = tc_smem(bars);
+    const uint32_t kv_full0 = tc_smem(bars + 1), kv_empty0 = tc_smem(bars + 1 + ATC_STAGES);
+    const uint32_t s_full0 = tc_smem(bars + 1 + 2 * ATC_STAGES), p_full0 = s_full0 + 16;
+    const uint32_t o_full = p_full0 + 16, o_free = o_full + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 2 * ATC_STAGES + 6);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int kvh = head / (p.nq / p.nkv);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < ATC_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(p_full0 + 8 * s, 4); }
+        mbar_init(o_full, 1);
+        mbar_init(o_free, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(tc_smem(tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 128;
+
+    pdl_wait();
+    pdl_trigger();
+    const int r = p.tiles[2 * tile], q0 = p.tiles[2 * tile + 1];
+    const int row_tokens = p.row_start[r + 1] - p.row_start[r];
+    const int n_q = min(ATC_BM, row_tokens - q0);
+    const int tok0 = p.row_start[r] + q0;
+    const int pos0 = p.row_pos[r] + q0;
+    const int hi = pos0 + n_q;                                           // keys < hi are read by the tile
+    int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    lo &= ~(ATC_BN - 1);                                                 // blocks start at multiples of 64 keys
+    const int nb = (hi - lo + ATC_BN - 1) / ATC_BN;
+
+    if (warp == 4 && lane == 0) {
+        // ---------------------------------------------------------------- producer
+        mbar_expect_tx(q_full, ATC_Q_BYTES);
+        tma_load_2d(tc_smem(sQ), &map_q, q_full, head * ATC_D, tok0);
+        tma_load_2d(tc_smem(sQ) + ATC_BM * 128, &map_q, q_full, head * ATC_D + 64, tok0);
+        const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
+        const int P = 1 << p.logP;
+        const int rows_per_op = P < ATC_BN ? P : ATC_BN;               // rows one TMA box brings
+        for (int j = 0; j < nb; ++j) {
+            const int s = j % ATC_STAGES;
+            if (!mbar_wait(kv_empty0 + 8 * s, ((j / ATC_STAGES) & 1) ^ 1)) { atomicExch(&g_attn_tc_error, 1); break; }
+            mbar_expect_tx(kv_full0 + 8 * s, ATC_STAGE_BYTES);
+            const uint32_t base = tc_smem(sKV + s * ATC_STAGE_BYTES);
+            for (int k0 = 0; k0 < ATC_BN; k0 += rows_per_op) {
+                int key = lo + j * ATC_BN + k0;
+                // Rows no query of the tile may see (beyond the last query, or in pages a windowed
+                // request has given back) are masked later: bring any rows that exist instead.
+                if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));
+                if (key < (p.page_base[r] << p.logP)) key = p.page_base[r] << p.logP;
+                const int page = table[key >> p.logP];
+                const int row = ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
+                const uint32_t off = (uint32_t)k0 * 128;
+                tma_load_2d(base + off, &map_k, kv_full0 + 8 * s, 0, row);
+                tma_load_2d(base + ATC_KV_HALF + off, &map_k, kv_full0 + 8 * s, 64, row);
+                tma_load_2d(base + 2 * ATC_KV_HALF + off, &map_v, kv_full0 + 8 * s, 0, row);
+                tma_load_2d(base + 3 * ATC_KV_HALF + off, &map_v, kv_full0 + 8 * s, 64, row);
+            }
+        }
+    } else if (warp == 5 && lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ATC_BN >> 3) << 17) |
+                                      ((uint32_t)(ATC_BM >> 4) << 24);
+        constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      ((uint32_t)(ATC_D >> 3) << 17) | ((uint32_t)(ATC_BM >> 4) << 24);
+        bool good = mbar_wait(q_full, 0);
+        if (!good) atomicExch(&g_attn_tc_error, 2);
+        auto issue_qk = [&](int j) {
+            const int s = j % ATC_STAGES;
+            if (!mbar_wait(kv_full0 + 8 * s, (j / ATC_STAGES) & 1)) { atomicExch(&g_attn_tc_error, 3); good = false; return; }
+            tc_fence_after();
+            const uint32_t kb = tc_smem(sKV + s * ATC_STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < ATC_D / 16; ++k) {
+                const uint32_t half = k >> 2, kk = k & 3;
+                umma_bf16(tmem_s0 + (j & 1) * ATC_BN, umma_desc(tc_smem(sQ) + half * ATC_BM * 128) + 2 * kk,
+                          umma_desc(kb + half * ATC_KV_HALF) + 2 * kk, IDESC_QK, k > 0 ? 1u : 0u);
+            }
+            umma_commit(s_full0 + 8 * (j & 1));
+        };
+        if (good && nb > 0) issue_qk(0);
+        for (int j = 0; j < nb && good; ++j) {
+            if (j + 1 < nb) issue_qk(j + 1);
+            if (!good) break;
+            if (!mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 4); break; }
+            if (j > 0 && !mbar_wait(o_free, (j - 1) & 1)) { atomicExch(&g_attn_tc_error, 5); break; }
+            tc_fence_after();
+            const int s = j % ATC_STAGES;
+            const uint32_t vb = tc_smem(sKV + s * ATC_STAGE_BYTES) + 2 * ATC_KV_HALF;
+            const uint32_t pb = tc_smem(sP + (j & 1) * ATC_P_BYTES);
+#pragma unroll
+            for (int k = 0; k < ATC_BN / 16; ++k)       // 16 keys a step: P advances 32 bytes, V 16 rows of 128 bytes
+                umma_bf16(tmem_o, umma_desc(pb) + 2 * k, umma_desc_mn(vb + k * 16 * 128, ATC_KV_HALF), IDESC_PV,
+                          k > 0 ? 1u : 0u);
+            umma_commit(kv_empty0 + 8 * s);
+            umma_commit(o_full);
+        }
+    } else if (warp < 4) {
+        // ---------------------------------------------------------------- softmax and output
+        const int row = threadIdx.x;                                     // query row = TMEM lane
+        const int qpos = pos0 + row;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        float acc[ATC_D];
+#pragma unroll
+        for (int i = 0; i < ATC_D; ++i) acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool good = true;
+        for (int j = 0; j < nb; ++j) {
+            if (good && !mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
+            good = __all_sync(0xffffffffu, good);
+            if (!good) break;
+            tc_fence_after();
+            const int key0 = lo + j * ATC_BN;
+            float s[ATC_BN];
+            {
+                float part[32];
+                tmem_ld32(tmem_s0 + lane_addr + (j & 1) * ATC_BN, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[i] = part[i];
+                tmem_ld32(tmem_s0 + lane_addr + (j & 1) * ATC_BN + 32, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < ATC_BN; ++c) {
+                const int key = key0 + c;
+                const bool okk = key <= qpos && row < n_q && (p.window <= 0 || key > qpos - p.window);
+                s[c] = okk ? s[c] * p.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, s[c]);
+            }
+            const float mn = fmaxf(m_run, mx);
+            const float mref = mn == -INFINITY ? 0.f : mn;
+            const float corr = exp2f(m_run - mref);
+            m_run = mn;
+            float psum = 0.f;
+            uint8_t* prow = sP + (j & 1) * ATC_P_BYTES + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {                              // 8 chunks of 8 keys (16 bytes)
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float a = exp2f(s[ch * 8 + 2 * q] - mref), b = exp2f(s[ch * 8 + 2 * q + 1] - mref);
+                    psum += a + b;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+                    w[q] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l_run = l_run * corr + psum;
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full0 + 8 * (j & 1));
+            // the block's P V
+            if (!mbar_wait(o_full, j & 1)) { atomicExch(&g_attn_tc_error, 7); good = false; }
+            good = __all_sync(0xffffffffu, good);
+            if (!good) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < ATC_D; c += 32) {
+                float part[32];
+                tmem_ld32(tmem_o + lane_addr + c, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * corr + part[i];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_free);
+        }
+        if (good && row < n_q) {
+            const float inv = 1.f / l_run;
+            bf16* orow = p.out + ((int64_t)(tok0 + row) * p.nq + head) * ATC_D;
+#pragma unroll
+            for (int c = 0; c < ATC_D; c += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(acc[c + 2 * q] * inv, acc[c + 2 * q + 1] * inv);
+                    w[q] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(256u) : "memory");
+    }
+}
+
+// What this kernel takes: head size 128, page size a power of two >= 8, bf16.
+extern "C" int acorn_attention_prefill_tc_supported(int nq, int nkv, int d, int P) {
+    return nkv > 0 && nq % nkv == 0 && nq <= 65535 && d == ATC_D && P >= 8 && (P & (P - 1)) == 0;
+}
+
+// q: [tokens, q_stride] bf16 (query heads first); k_pages / v_pages: [pages, nkv, P, 128] bf16.
+extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int tokens, void* out, const void* k_pages,
+                                          const void* v_pages, int64_t num_pages, const int* block_table,
+                                          const int* page_base, int table_stride, const int* row_start,
+                                          const int* row_pos, const int* tiles, int n_tiles, int nq, int nkv, int d,
+                                          int P, float scale, int window, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!acorn_attention_prefill_tc_supported(nq, nkv, d, P) || q_stride % 8 != 0 || ((uintptr_t)q & 15))
+        return ACORN_ERR_UNSUPPORTED;
+    AttnTcParams p;
+    p.out = (bf16*)out; p.block_table = block_table; p.page_base = page_base; p.row_start = row_start;
+    p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
+    p.logP = acorn_log2_exact_tc(P); p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map(&mq, q, tokens, (int64_t)nq * d, q_stride, 64, ATC_BM);
+    if (rc) return rc;
+    const int box_rows = P < ATC_BN ? P : ATC_BN;
+    rc = make_map(&mk, k_pages, num_pages * nkv * P, d, d, 64, box_rows);
+    if (rc) return rc;
+    rc = make_map(&mv, v_pages, num_pages * nkv * P, d, d, 64, box_rows);
+    if (rc) return rc;
+    const size_t smem = ATC_SMEM_TILES + (1 + 2 * ATC_STAGES + 6) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return acorn_launch(attention_prefill_tc_kernel, dim3(n_tiles, nq), dim3(ATC_THREADS), smem, stream, mq, mk, mv, p);
+}
+
+extern "C" int acorn_attention_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
+    return v;
+}

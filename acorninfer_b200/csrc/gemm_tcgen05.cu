@@ -20,16 +20,14 @@
 // Every wait on an mbarrier is bounded: when a wait gives up, the kernel records where in
 // g_gemm_tc_error, skips the rest of its work, still frees its tensor memory and returns.
 #include <cooperative_groups.h>
-#include <cuda.h>
 
-#include "common.cuh"
+#include "tcgen05_helpers.cuh"
 
 namespace cg = cooperative_groups;
 
 #define TC_BM 128            // rows of W per CTA (MMA M)
 #define TC_BK 64             // elements of K per stage (one 128-byte swizzle row)
 #define TC_THREADS 128
-#define TC_WAIT_LIMIT (1u << 22)
 
 __device__ int g_gemm_tc_error = 0;
 
@@ -54,72 +52,6 @@ struct TcParams {
     const float* norm_w;     // [N]
     float* ss_out;           // [ceil(N / 128), M]
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-
-__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
-}
-
-// Bounded wait for the phase with the given parity; false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t tries = 0; tries < TC_WAIT_LIMIT; ++tries) {
-        uint32_t ok;
-        asm volatile(
-            "{\n .reg .pred P1;\n mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n selp.u32 %0, 1, 0, P1;\n}\n"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        :: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
-// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups are
-// 1024 bytes apart (stride offset), descriptor version 1 (Blackwell), layout type 2.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;                       // leading offset: 1 (unused for swizzled K-major)
-    d |= (uint64_t)((1024 >> 4) & 0x3FFF) << 32;  // stride offset
-    d |= (uint64_t)1 << 46;                       // version
-    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
-    return d;
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 // ------------------------------------------------------------------ the kernel
 
@@ -335,37 +267,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
 
 // ------------------------------------------------------------------ host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
-// 2-D bf16 tensor [rows, K] with row stride ld elements; box = [box_rows, 64] with 128-byte swizzle.
-// Elements outside the tensor read as zero.
-static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return ACORN_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
-}
-
 template <int MB, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t stream) {
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
@@ -421,9 +322,9 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
     if (splits > p.kblocks) splits = p.kblocks;
     const int mb = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     CUtensorMap mw, mx;
-    int rc = make_map(&mw, w, N, K, ldw, TC_BM);
+    int rc = make_map(&mw, w, N, K, ldw, TC_BK, TC_BM);
     if (rc) return rc;
-    rc = make_map(&mx, x, M, K, ldx, mb);
+    rc = make_map(&mx, x, M, K, ldx, TC_BK, mb);
     if (rc) return rc;
     switch (mb) {
         case 16: return launch_tc<16, 6>(mw, mx, p, splits, stream);

@@ -61,6 +61,8 @@ class StepPlan:
     q_tiles: np.ndarray = None  # [n_tiles, 2]: (row, first token within the row) of each 64-token query tile
                                 # of the rows that bring more than one token
     single_tokens: np.ndarray = None   # flat indices of the tokens of single-token rows (decoded tokens)
+    q_tiles_large: np.ndarray = None   # the same rows cut for kernels with TILE_LARGE queries a tile:
+    q_tiles_small: np.ndarray = None   # rows of at least LARGE_MIN tokens in large tiles, shorter ones in Q_TILE tiles
 
     @property
     def num_logits(self) -> int:
@@ -68,6 +70,8 @@ class StepPlan:
 
 
 Q_TILE = 64     # query tokens per tile of the prefill attention kernel
+TILE_LARGE = 128   # query tokens per tile of the tcgen05 prefill attention kernel
+LARGE_MIN = 32     # rows shorter than this stay with the small-tile kernel
 
 
 def _table_stride(pages: int) -> int:
@@ -148,9 +152,12 @@ def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
     # falls back to the plain kernel for all tokens.
     tiles = [(r, q0) for r, n in enumerate(lens) if n > 1 for q0 in range(0, n, Q_TILE)]
     singles = [int(row_start[r]) for r, n in enumerate(lens) if n == 1]
+    large = [(r, q0) for r, n in enumerate(lens) if n >= LARGE_MIN for q0 in range(0, n, TILE_LARGE)]
+    small = [(r, q0) for r, n in enumerate(lens) if 1 < n < LARGE_MIN for q0 in range(0, n, Q_TILE)]
+    as_tiles = lambda t: np.asarray(t, np.int32).reshape(-1, 2)
     return StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
                     np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens),
-                    np.asarray(tiles, np.int32).reshape(-1, 2), np.asarray(singles, np.int32))
+                    as_tiles(tiles), np.asarray(singles, np.int32), as_tiles(large), as_tiles(small))
 
 
 # --------------------------------------------------------------------------- device side
@@ -181,6 +188,8 @@ class StepInputs:
     plan: StepPlan
     q_tiles: object = None
     single_tokens: object = None
+    q_tiles_large: object = None
+    q_tiles_small: object = None
     scratch: dict = field(default_factory=dict)     # per-step products shared by parts (e.g. split plans)
 
     @property
@@ -227,6 +236,8 @@ class StepWorkspace:
         put("logit_tokens", plan.num_logits)
         put("q_tiles", plan.q_tiles.size)
         put("single_tokens", plan.single_tokens.size)
+        put("q_tiles_large", plan.q_tiles_large.size)
+        put("q_tiles_small", plan.q_tiles_small.size)
         for i, g in enumerate(plan.groups):
             put(f"g{i}.kv_len", R)
             put(f"g{i}.page_base", R)
@@ -247,7 +258,8 @@ class StepWorkspace:
             "token_ids": plan.token_ids, "positions": plan.positions, "token_row": plan.token_row,
             "row_start": plan.row_start, "row_pos": plan.row_pos, "row_slot": plan.row_slot,
             "logit_tokens": plan.logit_tokens, "q_tiles": plan.q_tiles.reshape(-1),
-            "single_tokens": plan.single_tokens,
+            "single_tokens": plan.single_tokens, "q_tiles_large": plan.q_tiles_large.reshape(-1),
+            "q_tiles_small": plan.q_tiles_small.reshape(-1),
         }
         for gi, g in enumerate(plan.groups):
             arrays[f"g{gi}.kv_len"] = g.kv_len
@@ -271,4 +283,5 @@ class StepWorkspace:
             groups.append(GroupInputs(view(f"g{gi}.kv_len"), view(f"g{gi}.page_base"), bt, g.max_kv_len))
         return StepInputs(plan.num_tokens, plan.num_rows, view("token_ids"), view("positions"), view("token_row"),
                           view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan,
-                          view("q_tiles").view(-1, 2), view("single_tokens"))
+                          view("q_tiles").view(-1, 2), view("single_tokens"), view("q_tiles_large").view(-1, 2),
+                          view("q_tiles_small").view(-1, 2))

@@ -45,7 +45,17 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
             # decode kernel, both writing their rows of one output
             out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
-            if inputs.q_tiles.shape[0]:
+            if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
+                # long rows on the tcgen05 kernel (tiles of 128 queries), short ones on the mma.sync kernel
+                if inputs.q_tiles_large.shape[0]:
+                    ops.attention_prefill_tc(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
+                                             group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles_large,
+                                             inputs.num_tokens, nq, nkv, d, scale, window, out=out)
+                if inputs.q_tiles_small.shape[0]:
+                    ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
+                                          group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles_small,
+                                          inputs.num_tokens, nq, nkv, d, scale, window, out=out)
+            elif inputs.q_tiles.shape[0]:
                 ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                       group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles,
                                       inputs.num_tokens, nq, nkv, d, scale, window, out=out)

@@ -94,10 +94,16 @@ def bench_attn_prefill(a) -> None:
     row_pos = torch.zeros(1, dtype=torch.int32, device=DEV)
     tiles = torch.tensor([(0, q0) for q0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
-    us = _time([lambda: ops.attention_prefill(qkv, qkv.stride(0), k_pages, v_pages, table, base, row_start, row_pos,
-                                              tiles, T, nq, nkv, d, d ** -0.5, None)], a.reps, a.graph)
+    if a.kernel == "tc":
+        tiles = torch.tensor([(0, q0) for q0 in range(0, T, 128)], dtype=torch.int32, device=DEV)
+        fn = lambda: ops.attention_prefill_tc(qkv, qkv.stride(0), k_pages, v_pages, table, base, row_start, row_pos,
+                                              tiles, T, nq, nkv, d, d ** -0.5, None)
+    else:
+        fn = lambda: ops.attention_prefill(qkv, qkv.stride(0), k_pages, v_pages, table, base, row_start, row_pos,
+                                           tiles, T, nq, nkv, d, d ** -0.5, None)
+    us = _time([fn], a.reps, a.graph)
     fl = nq * d * 4.0 * (T * (T + 1) / 2)
-    print(f"attention_prefill tokens={T} heads={nq}/{nkv} d={d} page={P}: {us:.1f} us, {fl / us / 1e6:.0f} TFLOPS (causal)")
+    print(f"attention_prefill[{a.kernel}] tokens={T} heads={nq}/{nkv} d={d} page={P}: {us:.1f} us, {fl / us / 1e6:.0f} TFLOPS (causal)")
 
 
 def main(argv=None) -> int:
@@ -124,6 +130,7 @@ def main(argv=None) -> int:
         s.add_argument("--context", type=int, default=4096)
         s.add_argument("--tokens", type=int, default=2048)
         s.add_argument("--splits", type=int, default=0)
+        s.add_argument("--kernel", default="mma", choices=["mma", "tc"], help="prefill: mma.sync or tcgen05 kernel")
     a = p.parse_args(argv)
     {"gemm": bench_gemm, "attn-decode": bench_attn_decode, "attn-prefill": bench_attn_prefill}[a.what](a)
     return 0

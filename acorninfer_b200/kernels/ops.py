@@ -64,6 +64,11 @@ class _Sigs:
     acorn_attention_prefill_supported = [c_int, c_int, c_int]
     acorn_gemm_tc = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                      c_void_p]
+    acorn_attention_prefill_tc = [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_int, c_void_p]
+    acorn_attention_prefill_tc_supported = [c_int, c_int, c_int, c_int]
+    acorn_attention_tc_error = []
     acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                         c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
@@ -322,6 +327,44 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
                                       num_heads, num_kv_heads, head_dim, k_pages.shape[2], float(scale),
                                       int(window or 0), _stream()), "attention_prefill")
     return out
+
+
+def attention_prefill_tc_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return bool(lib().acorn_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim, page_size))
+
+
+def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                         block_table: torch.Tensor, page_base: torch.Tensor, row_start: torch.Tensor,
+                         row_pos: torch.Tensor, tiles: torch.Tensor, num_tokens: int, num_heads: int,
+                         num_kv_heads: int, head_dim: int, scale: float, window: int | None,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+    """tcgen05/TMA prefill attention (bfloat16, head size 128) for the query tiles listed in
+    ``tiles`` (int32 [n, 2]: row, first token within the row; 128 tokens a tile at most)."""
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc takes bfloat16")
+    _check(k_pages, "k_pages", q.dtype, 4)
+    _check(v_pages, "v_pages", q.dtype, 4)
+    if not attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim, k_pages.shape[2]):
+        raise KernelError(f"attention_prefill_tc does not take nq={num_heads}, nkv={num_kv_heads}, d={head_dim}, "
+                          f"page={k_pages.shape[2]}")
+    if q_stride % 8 or q.data_ptr() % 16:
+        raise KernelError("attention_prefill_tc: q rows must be 16-byte aligned")
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(tiles, "tiles", torch.int32, 2)
+    if out is None:
+        out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _ok(lib().acorn_attention_prefill_tc(q.data_ptr(), q_stride, num_tokens, out.data_ptr(), k_pages.data_ptr(),
+                                         v_pages.data_ptr(), k_pages.shape[0], block_table.data_ptr(),
+                                         page_base.data_ptr(), block_table.stride(0), row_start.data_ptr(),
+                                         row_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], num_heads,
+                                         num_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window or 0),
+                                         _stream()), "attention_prefill_tc")
+    return out
+
+
+def attention_tc_error() -> int:
+    """0, or where a bounded wait inside the tcgen05 attention kernel gave up since the last call."""
+    return int(lib().acorn_attention_tc_error())
 
 
 # ------------------------------------------------------------------ matrix products

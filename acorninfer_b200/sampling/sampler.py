@@ -20,6 +20,16 @@ from .params import SamplingParams
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
+        self._greedy: dict[int, tuple] = {}      # rows -> constant parameter tensors of an all-greedy step
+
+    def _greedy_params(self, R: int):
+        got = self._greedy.get(R)
+        if got is None:
+            z = lambda dt: torch.zeros(R, dtype=dt, device=self.device)
+            got = (z(torch.float32), z(torch.int32), torch.ones(R, dtype=torch.float32, device=self.device),
+                   z(torch.int64), z(torch.int64))
+            self._greedy[R] = got
+        return got
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams], counters: list[int],
                want_logprobs: bool = False) -> tuple[list[int], list[float] | None]:
@@ -27,14 +37,16 @@ class Sampler:
         R = logits.shape[0]
         if len(params) != R or len(counters) != R:
             raise ValueError("one SamplingParams and one counter per logits row")
-        host = torch.empty((5, R), dtype=torch.float64)
-        for i, (p, c) in enumerate(zip(params, counters)):
-            host[0, i], host[1, i], host[2, i] = p.temperature, p.top_k, p.top_p
-        dev = host.to(self.device, non_blocking=False)
-        seeds = torch.tensor([p.seed & (2 ** 63 - 1) for p in params], dtype=torch.int64).to(self.device)
-        ctrs = torch.tensor([int(c) for c in counters], dtype=torch.int64).to(self.device)
-        tokens, logprobs = ops.sample(logits, dev[0].float().contiguous(), dev[1].to(torch.int32).contiguous(),
-                                      dev[2].float().contiguous(), seeds, ctrs, want_logprobs)
+        if all(p.greedy for p in params):
+            temperature, top_k, top_p, seeds, ctrs = self._greedy_params(R)
+        else:
+            dev = self.device
+            temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32).to(dev, non_blocking=True)
+            top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(dev, non_blocking=True)
+            top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32).to(dev, non_blocking=True)
+            seeds = torch.tensor([p.seed & (2 ** 63 - 1) for p in params], dtype=torch.int64).to(dev, non_blocking=True)
+            ctrs = torch.tensor([int(c) for c in counters], dtype=torch.int64).to(dev, non_blocking=True)
+        tokens, logprobs = ops.sample(logits, temperature, top_k, top_p, seeds, ctrs, want_logprobs)
         toks = tokens.tolist()
         if any(t < 0 for t in toks):
             raise ValueError("logits contain NaN or infinity: the model's forward pass is broken")

@@ -203,3 +203,24 @@ def test_attention_prefill_kernel(nq, nkv, d, P, window):
     plain_out = ops().attention_plain(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
                                       lay["token_row"], lay["positions"], sum(qlens), nq, nkv, d, d ** -0.5, window)
     assert torch.allclose(out.float(), plain_out.float(), **BF16_TOL)
+
+
+@pytest.mark.parametrize("nq,nkv,P,window", [(32, 8, 16, None), (4, 4, 8, None), (6, 2, 64, None), (8, 1, 16, 200),
+                                             (2, 1, 128, None)])
+def test_attention_prefill_tcgen05_kernel(nq, nkv, P, window):
+    """The tcgen05/TMA prefill kernel (head size 128): portions that start inside a request and inside
+    a page, tiles that end inside a page, rows shorter than a tile, a far key that decides."""
+    d = 128
+    before = [0, 130, 77, 500, 31, 1000]
+    qlens = [300, 128, 129, 40, 65, 32]
+    lay, wide, k_pages, v_pages, row_start, row_pos, _, want = build_case(before, qlens, nq, nkv, d, P, window, 200, 6,
+                                                                         standout_row=3)
+    tiles = torch.tensor([(r, q0) for r, n in enumerate(qlens) for q0 in range(0, n, 128)], dtype=torch.int32,
+                         device=DEV).view(-1, 2)
+    out = ops().attention_prefill_tc(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                     row_start, row_pos, tiles, sum(qlens), nq, nkv, d, d ** -0.5, window)
+    assert ops().attention_tc_error() == 0
+    assert torch.allclose(out.double().cpu(), want, **BF16_TOL)
+    again = ops().attention_prefill_tc(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                       row_start, row_pos, tiles, sum(qlens), nq, nkv, d, d ** -0.5, window)
+    assert torch.equal(out, again)

@@ -28,7 +28,12 @@ TINY_C = dict(cfg=Qwen3Config(num_hidden_layers=2, hidden_size=120, num_attentio
                               head_dim=48, intermediate_size=200, rms_norm_eps=3e-6, rope_theta=5e5, vocab_size=331,
                               tie_word_embeddings=False, bos_token_id=None, eos_token_id=()),
               sigma=0.04, sigma_norm=0.2, seed=303, page_size=16)
-TINIES = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+# head size 128: the size the tcgen05 attention kernel takes, so that replay runs through it
+TINY_D = dict(cfg=Qwen3Config(num_hidden_layers=2, hidden_size=192, num_attention_heads=4, num_key_value_heads=2,
+                              head_dim=128, intermediate_size=320, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=500,
+                              tie_word_embeddings=False, bos_token_id=None, eos_token_id=()),
+              sigma=0.04, sigma_norm=0.1, seed=404, page_size=16)
+TINIES = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
 
 
 def make_model_dir(tmp: Path, tiny: dict, dtype=torch.bfloat16) -> Path:
