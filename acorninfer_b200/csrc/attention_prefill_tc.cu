@@ -1,17 +1,20 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05), head size 128, bfloat16:
 // causal attention of a tile of 128 consecutive queries of one request against its keys and
-// values in the paged cache, S = Q K^T and P V computed by tcgen05.mma with the accumulators
+// values in the paged cache, S = Q K^T and O += P V computed by tcgen05.mma with the accumulators
 // in tensor memory, K/V/Q tiles brought by TMA through the block table.
 //
-// One CTA per (tile of 128 queries, query head), 6 warps:
+// One CTA per (tile of 128 queries, query head), 6 warps, two CTAs to an SM:
 //   warps 0-3  softmax: thread r owns query row r (= TMEM lane r): reads its row of S with
-//              tcgen05.ld, masks by absolute position (causal, window), online softmax in
-//              float32 base 2, writes P (bfloat16) into a swizzled shared-memory tile, then adds
-//              the block's P V (read from TMEM) into its 128 float32 output accumulators.
+//              tcgen05.ld, masks by absolute position (causal, window) where a block needs it,
+//              exponentiates in float32 base 2 against a reference maximum, writes P (bfloat16)
+//              into a swizzled shared-memory tile.  O stays in tensor memory across blocks; it
+//              is rescaled (tcgen05.ld / st) only when a row's maximum has grown by more than
+//              2^8 since its reference was set, so most blocks skip that pass.  At the end the
+//              thread reads its row of O, divides by the row sum and writes the output.
 //   warp 4     producer: TMA loads of Q (once) and, per block of 64 keys, of the K and V page
 //              tiles ((page, kv head) tiles are contiguous [page_size x 128] in the cache).
-//   warp 5     MMA issuer: S[j] = Q K_j^T into one of two S buffers (so the next block's scores
-//              are computed while the softmax warps work on this one), O_j = P_j V_j.
+//   warp 5     MMA issuer: S[j] = Q K_j^T into one of two S buffers (the next block's scores are
+//              computed while the softmax warps work on this one), then O += P_j V_j.
 // Tensor memory: S0, S1 (64 columns each), O (128 columns).  V is the MN-major B operand of the
 // second product (head dims contiguous); P is a K-major A operand written by the softmax
 // warps (generic proxy) and fenced to the async proxy.
@@ -23,8 +26,9 @@
 #define ATC_D 128
 #define ATC_BM 128
 #define ATC_BN 64
-#define ATC_STAGES 3
+#define ATC_STAGES 2
 #define ATC_THREADS 192
+#define ATC_RESCALE_LOG2 8.0f     // rescale O only when the row maximum grew by more than this (base 2)
 
 __device__ int g_attn_tc_error = 0;
 
@@ -39,40 +43,45 @@ struct AttnTcParams {
     float scale_log2;
 };
 
-// shared memory map (bytes, all tile regions 1024-aligned)
+// shared memory map (bytes; the tile regions are 1024-aligned)
 #define ATC_Q_BYTES (2 * ATC_BM * 128)                    // two 64-element halves of [128 x 128]
 #define ATC_KV_HALF (ATC_BN * 128)                         // one half of a K or V block: [64 keys x 64 dims]
 #define ATC_STAGE_BYTES (4 * ATC_KV_HALF)                  // K half 0, K half 1, V half 0, V half 1
 #define ATC_P_BYTES (ATC_BM * 128)                         // [128 rows x 64 keys] bf16
-#define ATC_SMEM_TILES (ATC_Q_BYTES + ATC_STAGES * ATC_STAGE_BYTES + 2 * ATC_P_BYTES)
+#define ATC_SMEM_TILES (ATC_Q_BYTES + ATC_STAGES * ATC_STAGE_BYTES + ATC_P_BYTES)
+#define ATC_NUM_BARS (1 + 2 * ATC_STAGES + 2 + 1 + 1)      // q_full, kv_full/empty, s_full[2], p_full, o_done
 
-__global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                               const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v,
                                                                               const AttnTcParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + ATC_Q_BYTES;
     uint8_t* sP = sKV + ATC_STAGES * ATC_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATC_P_BYTES);
-    // q_full, kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full, o_free
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + ATC_P_BYTES);
     const uint32_t q_full = tc_smem(bars);
     const uint32_t kv_full0 = tc_smem(bars + 1), kv_empty0 = tc_smem(bars + 1 + ATC_STAGES);
-    const uint32_t s_full0 = tc_smem(bars + 1 + 2 * ATC_STAGES), p_full0 = s_full0 + 16;
-    const uint32_t o_full = p_full0 + 16, o_free = o_full + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1 + 2 * ATC_STAGES + 6);
+    const uint32_t s_full0 = tc_smem(bars + 1 + 2 * ATC_STAGES);
+    const uint32_t p_full = s_full0 + 16, o_done = p_full + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + ATC_NUM_BARS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, head = blockIdx.y;
+    // tiles are listed by rising position within a request; the late tiles read the most keys, so
+    // they are started first
+    const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
     const int kvh = head / (p.nq / p.nkv);
+    if (tc_smem(smem) & 1023u) {            // the swizzled tiles need a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 9);
+        return;
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < ATC_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(s_full0 + 8 * s, 1); mbar_init(p_full0 + 8 * s, 4); }
-        mbar_init(o_full, 1);
-        mbar_init(o_free, 4);
+        for (int s = 0; s < 2; ++s) mbar_init(s_full0 + 8 * s, 1);
+        mbar_init(p_full, 4);
+        mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -106,6 +115,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
         const int P = 1 << p.logP;
         const int rows_per_op = P < ATC_BN ? P : ATC_BN;               // rows one TMA box brings
+        const int first_key = p.page_base[r] << p.logP;
         for (int j = 0; j < nb; ++j) {
             const int s = j % ATC_STAGES;
             if (!mbar_wait(kv_empty0 + 8 * s, ((j / ATC_STAGES) & 1) ^ 1)) { atomicExch(&g_attn_tc_error, 1); break; }
@@ -116,7 +126,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                 // Rows no query of the tile may see (beyond the last query, or in pages a windowed
                 // request has given back) are masked later: bring any rows that exist instead.
                 if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));
-                if (key < (p.page_base[r] << p.logP)) key = p.page_base[r] << p.logP;
+                if (key < first_key) key = first_key;
                 const int page = table[key >> p.logP];
                 const int row = ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
                 const uint32_t off = (uint32_t)k0 * 128;
@@ -149,30 +159,29 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         };
         if (good && nb > 0) issue_qk(0);
         for (int j = 0; j < nb && good; ++j) {
+            // S[(j+1) & 1] is free: the softmax warps read block j-1 from it before they signalled
+            // p_full for j-1.  With two K/V stages the tiles of block j+1 arrive after P V of block
+            // j-1 has completed; the other CTA of the SM computes meanwhile.
             if (j + 1 < nb) issue_qk(j + 1);
             if (!good) break;
-            if (!mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 4); break; }
-            if (j > 0 && !mbar_wait(o_free, (j - 1) & 1)) { atomicExch(&g_attn_tc_error, 5); break; }
+            if (!mbar_wait(p_full, j & 1)) { atomicExch(&g_attn_tc_error, 4); break; }
             tc_fence_after();
             const int s = j % ATC_STAGES;
             const uint32_t vb = tc_smem(sKV + s * ATC_STAGE_BYTES) + 2 * ATC_KV_HALF;
-            const uint32_t pb = tc_smem(sP + (j & 1) * ATC_P_BYTES);
+            const uint32_t pb = tc_smem(sP);
 #pragma unroll
             for (int k = 0; k < ATC_BN / 16; ++k)       // 16 keys a step: P advances 32 bytes, V 16 rows of 128 bytes
                 umma_bf16(tmem_o, umma_desc(pb) + 2 * k, umma_desc_mn(vb + k * 16 * 128, ATC_KV_HALF), IDESC_PV,
-                          k > 0 ? 1u : 0u);
+                          (j > 0 || k > 0) ? 1u : 0u);
             umma_commit(kv_empty0 + 8 * s);
-            umma_commit(o_full);
+            umma_commit(o_done);
         }
     } else if (warp < 4) {
         // ---------------------------------------------------------------- softmax and output
         const int row = threadIdx.x;                                     // query row = TMEM lane
         const int qpos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        float acc[ATC_D];
-#pragma unroll
-        for (int i = 0; i < ATC_D; ++i) acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;
         bool good = true;
         for (int j = 0; j < nb; ++j) {
             if (good && !mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
@@ -190,65 +199,89 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
 #pragma unroll
                 for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
             }
+            // a block every query of the tile sees whole needs no mask
+            if (key0 + ATC_BN - 1 > pos0 || p.window > 0 || n_q < ATC_BM) {
+#pragma unroll
+                for (int c = 0; c < ATC_BN; ++c) {
+                    const int key = key0 + c;
+                    const bool okk = key <= qpos && row < n_q && (p.window <= 0 || key > qpos - p.window);
+                    s[c] = okk ? s[c] : -INFINITY;
+                }
+            }
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < ATC_BN; ++c) {
-                const int key = key0 + c;
-                const bool okk = key <= qpos && row < n_q && (p.window <= 0 || key > qpos - p.window);
-                s[c] = okk ? s[c] * p.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, s[c]);
+            for (int c = 0; c < ATC_BN; ++c) mx = fmaxf(mx, s[c]);
+            mx *= p.scale_log2;                                          // the scale is positive
+            // reference maximum: moved only when the row maximum outgrew it by more than 2^8
+            float corr = 1.f;
+            if (mx > m_ref + ATC_RESCALE_LOG2) {
+                corr = fast_exp2(m_ref - mx);                            // m_ref = -inf: 0
+                l_run *= corr;
+                m_ref = mx;
             }
-            const float mn = fmaxf(m_run, mx);
-            const float mref = mn == -INFINITY ? 0.f : mn;
-            const float corr = exp2f(m_run - mref);
-            m_run = mn;
+            const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
             float psum = 0.f;
-            uint8_t* prow = sP + (j & 1) * ATC_P_BYTES + row * 128;
+            uint32_t w[ATC_BN / 2];
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {                              // 8 chunks of 8 keys (16 bytes)
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float a = exp2f(s[ch * 8 + 2 * q] - mref), b = exp2f(s[ch * 8 + 2 * q + 1] - mref);
-                    psum += a + b;
-                    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-                    w[q] = *reinterpret_cast<uint32_t*>(&v);
-                }
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int c = 0; c < ATC_BN; c += 2) {
+                const float a = fast_exp2(fmaf(s[c], p.scale_log2, neg_ref));
+                const float b = fast_exp2(fmaf(s[c + 1], p.scale_log2, neg_ref));
+                psum += a + b;
+                __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+                w[c >> 1] = *reinterpret_cast<uint32_t*>(&v);
             }
-            l_run = l_run * corr + psum;
+            l_run += psum;
+            // P V of the block before has completed: the P tile is free and O is stable
+            if (j > 0) {
+                if (!mbar_wait(o_done, (j - 1) & 1)) { atomicExch(&g_attn_tc_error, 7); good = false; }
+                good = __all_sync(0xffffffffu, good);
+                if (!good) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+                    for (int c = 0; c < ATC_D; c += 32) {
+                        float part[32];
+                        tmem_ld32(tmem_o + lane_addr + c, part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) part[i] *= corr;
+                        tmem_st32(tmem_o + lane_addr + c, part);
+                    }
+                }
+            }
+            uint8_t* prow = sP + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)                                // 8 chunks of 8 keys (16 bytes), swizzled
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
+                    make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full0 + 8 * (j & 1));
-            // the block's P V
-            if (!mbar_wait(o_full, j & 1)) { atomicExch(&g_attn_tc_error, 7); good = false; }
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (good && nb > 0) {
+            if (!mbar_wait(o_done, (nb - 1) & 1)) { atomicExch(&g_attn_tc_error, 8); good = false; }
             good = __all_sync(0xffffffffu, good);
-            if (!good) break;
+        }
+        if (good) {
             tc_fence_after();
+            const float inv = row < n_q ? 1.f / l_run : 0.f;
+            bf16* orow = p.out + ((int64_t)(tok0 + row) * p.nq + head) * ATC_D;
 #pragma unroll
             for (int c = 0; c < ATC_D; c += 32) {
                 float part[32];
                 tmem_ld32(tmem_o + lane_addr + c, part);
+                if (row < n_q) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * corr + part[i];
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_free);
-        }
-        if (good && row < n_q) {
-            const float inv = 1.f / l_run;
-            bf16* orow = p.out + ((int64_t)(tok0 + row) * p.nq + head) * ATC_D;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t ww[4];
 #pragma unroll
-            for (int c = 0; c < ATC_D; c += 8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    __nv_bfloat162 v = __floats2bfloat162_rn(acc[c + 2 * q] * inv, acc[c + 2 * q + 1] * inv);
-                    w[q] = *reinterpret_cast<uint32_t*>(&v);
+                        for (int q = 0; q < 4; ++q) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(part[i + 2 * q] * inv, part[i + 2 * q + 1] * inv);
+                            ww[q] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(orow + c + i) = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+                    }
                 }
-                *reinterpret_cast<uint4*>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
@@ -285,7 +318,7 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
     if (rc) return rc;
     rc = make_map(&mv, v_pages, num_pages * nkv * P, d, d, 64, box_rows);
     if (rc) return rc;
-    const size_t smem = ATC_SMEM_TILES + (1 + 2 * ATC_STAGES + 6) * 8 + 16 + 1024;
+    const size_t smem = ATC_SMEM_TILES + ATC_NUM_BARS * 8 + 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
