@@ -96,9 +96,9 @@ def validate_entries(entries: list[StepEntry], vocab_size: int, max_tokens: int 
         seen.add(id(e.cache))
         if len(e.tokens) < 1:
             raise BatchError(f"request {rid!r} brings no tokens")
-        for t in e.tokens:
-            if not (0 <= int(t) < vocab_size):
-                raise BatchError(f"request {rid!r}: token id {t} outside the vocabulary (0..{vocab_size - 1})")
+        if min(e.tokens) < 0 or max(e.tokens) >= vocab_size:
+            bad = next(t for t in e.tokens if not (0 <= int(t) < vocab_size))
+            raise BatchError(f"request {rid!r}: token id {bad} outside the vocabulary (0..{vocab_size - 1})")
         for w in e.want:
             if not (0 <= int(w) < len(e.tokens)):
                 raise BatchError(f"request {rid!r}: wanted place {w} outside its {len(e.tokens)} tokens")

@@ -125,7 +125,7 @@ class Engine:
         try:
             entries, samplers = [], []
             for p in decision.portions:
-                ids = p.request.all_ids[p.start:p.start + p.length]
+                ids = p.request.tokens(p.start, p.length)
                 entries.append(StepEntry(p.request.cache, ids, [p.length - 1] if p.samples else []))
                 if p.samples:
                     samplers.append(p.request)

@@ -46,6 +46,16 @@ class Request:
     def all_ids(self) -> list[int]:
         return self.prompt_ids + self.generated_ids
 
+    def tokens(self, start: int, length: int) -> list[int]:
+        """``all_ids[start:start + length]`` without building the whole list."""
+        n_prompt = len(self.prompt_ids)
+        end = start + length
+        if end <= n_prompt:
+            return self.prompt_ids[start:end]
+        if start >= n_prompt:
+            return self.generated_ids[start - n_prompt:end - n_prompt]
+        return self.prompt_ids[start:] + self.generated_ids[:end - n_prompt]
+
     @property
     def is_finished(self) -> bool:
         return self.status is RequestStatus.FINISHED

@@ -1,0 +1,99 @@
+"""The step's host-side layout: validation before anything runs, and the arrays the kernels read."""
+
+import numpy as np
+import pytest
+import torch
+
+from acorninfer_b200.cache.manager import CacheManager
+from acorninfer_b200.engine.batch import BatchError, StepEntry, StepWorkspace, plan_step, validate_entries
+from acorninfer_b200.engine.request import Request
+from acorninfer_b200.parts.base import KVNeeds
+from acorninfer_b200.sampling.params import SamplingParams
+
+
+def manager(window=None):
+    needs = {0: KVNeeds(2, 16, None)}
+    if window:
+        needs[1] = KVNeeds(2, 16, window)
+    return CacheManager(needs, {}, 64, 4, 8, dtype=torch.float32, device="cpu", allocate=False)
+
+
+def test_a_bad_step_is_refused_before_anything_is_held():
+    m = manager()
+    a, b = m.open("a"), m.open("b")
+    ok = [StepEntry(a, [1, 2, 3], [2]), StepEntry(b, [4], [0])]
+    validate_entries(ok, vocab_size=10)
+    for bad, word in [([], "at least one"), ([StepEntry(a, [], [])], "no tokens"),
+                      ([StepEntry(a, [1, 10], [])], "outside the vocabulary"),
+                      ([StepEntry(a, [1, -1], [])], "outside the vocabulary"),
+                      ([StepEntry(a, [1, 2], [2])], "wanted place"),
+                      ([StepEntry(a, [1], []), StepEntry(a, [2], [])], "twice")]:
+        with pytest.raises(BatchError, match=word):
+            validate_entries(bad, vocab_size=10)
+    with pytest.raises(BatchError, match="workspace holds"):
+        validate_entries(ok, vocab_size=10, max_tokens=3)
+    m.close(b)
+    with pytest.raises(BatchError, match="closed"):
+        validate_entries([StepEntry(b, [1], [])], vocab_size=10)
+    assert m.free_pages() == [64]
+
+
+def test_plan_of_a_mixed_step():
+    m = manager(window=6)
+    a, b, c = m.open("a"), m.open("b"), m.open("c")
+    for rc, n in ((a, 9), (b, 70)):                  # a and b already hold tokens
+        m.extend(rc, n)
+        m.commit(rc, n)
+    entries = [StepEntry(a, [7], [0]), StepEntry(c, list(range(40)), [39, 0]), StepEntry(b, [3, 4], [])]
+    for e in entries:
+        m.extend(e.cache, e.cache.length + len(e.tokens))
+    plan = plan_step(entries, m)
+    assert plan.num_tokens == 43 and plan.num_rows == 3 and not plan.all_decode and plan.max_q_len == 40
+    assert plan.token_ids.tolist() == [7] + list(range(40)) + [3, 4]
+    assert plan.positions.tolist() == [9] + list(range(40)) + [70, 71]
+    assert plan.token_row.tolist() == [0] + [1] * 40 + [2, 2]
+    assert plan.row_start.tolist() == [0, 1, 41, 43] and plan.row_pos.tolist() == [9, 0, 70]
+    assert plan.row_slot.tolist() == [a.slot, c.slot, b.slot]
+    assert plan.logit_tokens.tolist() == [0, 40, 1]              # entries in order, then `want` in order
+    assert plan.single_tokens.tolist() == [0]                   # the decoded token of a
+    assert plan.q_tiles.tolist() == [[1, 0], [2, 0]]            # rows with more than one token, 64 queries a tile
+    assert plan.q_tiles_large.tolist() == [[1, 0]] and plan.q_tiles_small.tolist() == [[2, 0]]
+    full, win = plan.groups
+    assert full.kv_len.tolist() == [10, 40, 72] and full.page_base.tolist() == [0, 0, 0]
+    assert full.block_table.shape[1] >= 18 and full.block_table.shape[1] & (full.block_table.shape[1] - 1) == 0
+    assert full.block_table[2, :18].tolist() == b.tables[0]
+    # the windowed group has given the front pages of b back: its table starts at page_base
+    assert win.page_base.tolist() == [a.page_base[1], 0, b.page_base[1]] and b.page_base[1] > 0
+    assert win.block_table[2, :len(b.tables[1])].tolist() == b.tables[1]
+
+
+def test_layout_depends_on_the_shape_only_and_is_aligned():
+    m = manager()
+    rcs = [m.open(i) for i in range(3)]
+    for rc in rcs:
+        m.extend(rc, 5)
+        m.commit(rc, 5)
+
+    def decode_plan(tokens):
+        entries = [StepEntry(rc, [t], [0]) for rc, t in zip(rcs, tokens)]
+        for e in entries:
+            m.extend(e.cache, e.cache.length + 1)
+        plan = plan_step(entries, m)
+        for e in entries:
+            m.commit(e.cache, e.cache.length + 1)
+        return plan
+
+    p1, p2 = decode_plan([1, 2, 3]), decode_plan([4, 5, 6])
+    l1, n1 = StepWorkspace.layout(p1)
+    l2, n2 = StepWorkspace.layout(p2)
+    assert l1 == l2 and n1 == n2 and p1.all_decode                # same shape, same addresses: a graph can be replayed
+    assert all(off % 4 == 0 for off, _ in l1.values())            # every array starts on 16 bytes
+    names = list(l1)
+    assert all(l1[a][0] + l1[a][1] <= l1[b][0] for a, b in zip(names, names[1:]))   # no overlap
+
+
+def test_request_token_slices():
+    r = Request(0, [1, 2, 3, 4], SamplingParams(), 8, frozenset(), generated_ids=[5, 6, 7])
+    for start in range(7):
+        for length in range(1, 8 - start):
+            assert r.tokens(start, length) == r.all_ids[start:start + length]
