@@ -252,6 +252,16 @@ static int launch_decode(const DecodeParams& p, int n, cudaStream_t stream) {
     return acorn_launch(attention_decode_kernel<D>, grid, dim3(DEC_THREADS), smem, stream, p);
 }
 
+// The merge pass alone, for main passes that live in other files.
+extern "C" int acorn_attention_decode_merge(const float* part_o, const float* part_lse, void* out,
+                                            const int* token_list, int n, int nq, int d, int num_splits,
+                                            cudaStream_t stream) {
+    if (n <= 0 || num_splits <= 1) return 0;
+    if (num_splits > DEC_MAX_SPLITS || n > 65535 || nq > 65535) return ACORN_ERR_UNSUPPORTED;
+    return acorn_launch(attention_decode_merge_kernel, dim3(n, nq), dim3(d >= 128 ? 128 : 64), 0, stream, part_o,
+                        part_lse, (bf16*)out, token_list, nq, d, num_splits);
+}
+
 // Sizes this kernel takes: head_dim a multiple of 16 up to 128, or 256; nq / nkv <= 16.
 extern "C" int acorn_attention_decode_supported(int nq, int nkv, int d) {
     if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return 0;

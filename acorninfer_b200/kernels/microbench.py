@@ -77,9 +77,10 @@ def bench_attn_decode(a) -> None:
     qkv = torch.randn(B, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
     splits = a.splits or decode_splits(B, nkv, ctx)
     us = _time([lambda: ops.attention_decode(qkv, qkv.stride(0), k_pages, v_pages, table, base, rows, pos, B, nq, nkv,
-                                             d, d ** -0.5, None, splits)], a.reps, a.graph)
+                                             d, d ** -0.5, None, splits, use_tma=a.kernel != "mma")],
+               a.reps, a.graph)
     gb = B * ctx * nkv * d * 2 * 2 / 1e9
-    print(f"attention_decode B={B} context={ctx} heads={nq}/{nkv} d={d} page={P} splits={splits}: {us:.1f} us, "
+    print(f"attention_decode[{'cp.async' if a.kernel == 'mma' else 'tma'}] B={B} context={ctx} heads={nq}/{nkv} d={d} page={P} splits={splits}: {us:.1f} us, "
           f"{gb / us * 1e6:.0f} GB/s of K and V")
 
 

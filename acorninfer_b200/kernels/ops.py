@@ -58,6 +58,12 @@ class _Sigs:
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                               c_int, c_void_p, c_void_p, c_void_p]
     acorn_attention_decode_supported = [c_int, c_int, c_int]
+    acorn_attention_decode_tma_main = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                       c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    acorn_attention_decode_tma_supported = [c_int, c_int, c_int, c_int]
+    acorn_attention_decode_tma_error = []
+    acorn_attention_decode_merge = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_attention_prefill = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                c_void_p]
@@ -271,7 +277,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
                      block_table: torch.Tensor, page_base: torch.Tensor, token_row: torch.Tensor,
                      positions: torch.Tensor, num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
                      scale: float, window: int | None, num_splits: int, token_list: torch.Tensor | None = None,
-                     out: torch.Tensor | None = None, scratch: tuple | None = None) -> torch.Tensor:
+                     out: torch.Tensor | None = None, scratch: tuple | None = None,
+                     use_tma: bool | None = None) -> torch.Tensor:
     """Split-K decode attention (bfloat16) for single-token rows: the tokens 0..num_tokens-1, or
     those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
     not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
@@ -296,12 +303,31 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
         part_o, part_lse = scratch
         if part_o.numel() < n * num_heads * num_splits * head_dim or part_lse.numel() < n * num_heads * num_splits:
             raise KernelError("attention_decode: scratch too small")
+    P = k_pages.shape[2]
+    if use_tma is None:
+        use_tma = bool(lib().acorn_attention_decode_tma_supported(num_heads, num_kv_heads, head_dim, P))
+    if use_tma:
+        # head size 128: K/V tiles by TMA (attention_decode_tma.cu), then the common merge pass
+        _ok(lib().acorn_attention_decode_tma_main(
+            q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+            block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0), token_row.data_ptr(),
+            positions.data_ptr(), _ptr(token_list), n, num_heads, num_kv_heads, head_dim, P, float(scale),
+            int(window or 0), num_splits, _ptr(part_o), _ptr(part_lse), _stream()), "attention_decode_tma")
+        if num_splits > 1:
+            _ok(lib().acorn_attention_decode_merge(part_o.data_ptr(), part_lse.data_ptr(), out.data_ptr(),
+                                                   _ptr(token_list), n, num_heads, head_dim, num_splits, _stream()),
+                "attention_decode_merge")
+        return out
     _ok(lib().acorn_attention_decode(q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
                                      block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0),
                                      token_row.data_ptr(), positions.data_ptr(), _ptr(token_list), n, num_heads,
-                                     num_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window or 0),
+                                     num_kv_heads, head_dim, P, float(scale), int(window or 0),
                                      num_splits, _ptr(part_o), _ptr(part_lse), _stream()), "attention_decode")
     return out
+
+
+def attention_decode_tma_error() -> int:
+    return int(lib().acorn_attention_decode_tma_error())
 
 
 def attention_prefill(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
