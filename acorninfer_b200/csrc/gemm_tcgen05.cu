@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     } else {
         // TC_MODE_ADD_NORM: residual += product; out = bf16(residual * norm weight), not yet
         // scaled; this tile's share of sum(residual^2) per row goes to ss_out[tile][row]
-        constexpr int MAX_ROWS = MB <= 32 ? MB : 1;     // the host refuses this mode for larger tiles
+        constexpr int MAX_ROWS = MB <= 64 ? MB : 1;     // the host refuses this mode for larger tiles
         float sq[MAX_ROWS];
 #pragma unroll
         for (int i = 0; i < MAX_ROWS; ++i) {
@@ -304,17 +304,17 @@ extern "C" int acorn_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int64_t 
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && M <= (1 << 30);
 }
 
-// mode, ss_in .. ss_out: see TcParams.  Modes other than plain, and ss_in, are for at most 32 rows.
+// mode, ss_in .. ss_out: see TcParams.  Modes other than plain, and ss_in, are for at most 64 rows.
 extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
                                 int N, int K, int out_f32, int splits, int mode, const float* ss_in, int ss_parts,
                                 int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
                                 float* ss_out, cudaStream_t stream) {
     if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
-    if (mode != TC_MODE_PLAIN && (M > 32 || out_f32)) return ACORN_ERR_UNSUPPORTED;
+    if (mode != TC_MODE_PLAIN && (M > 64 || out_f32)) return ACORN_ERR_UNSUPPORTED;
     if (mode == TC_MODE_SWIGLU && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
     if (mode == TC_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
-    if (ss_in != nullptr && (M > 32 || ss_parts < 1 || norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
+    if (ss_in != nullptr && (M > 64 || ss_parts < 1 || norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
     TcParams p;
     p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.kblocks = (K + TC_BK - 1) / TC_BK; p.out_f32 = out_f32;
     p.mode = mode; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_width = norm_width; p.eps = eps;

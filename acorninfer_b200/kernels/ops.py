@@ -462,7 +462,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
             out: torch.Tensor | None = None, epilogue: AddNormEpilogue | None = None, swiglu: bool = False):
     """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
-    ``x`` may be ``NormedRows`` (at most 32 rows): the rows' RMS factors are applied to the product.
+    ``x`` may be ``NormedRows`` (at most 64 rows): the rows' RMS factors are applied to the product.
     ``epilogue``: see ``AddNormEpilogue`` (returns ``NormedRows``).  ``swiglu``: ``w`` holds blocks
     of 64 gate rows and 64 up rows; returns ``silu(gate) * up`` [M, N / 2]."""
     rows = x if isinstance(x, NormedRows) else None
@@ -474,8 +474,8 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
         raise KernelError("gemm_tc writes bfloat16 or float32")
     M, K = xt.shape
     N = w.shape[0]
-    if (rows is not None or epilogue is not None or swiglu) and M > 32:
-        raise KernelError(f"gemm_tc: fused norm / SwiGLU epilogues take at most 32 rows, got {M}")
+    if (rows is not None or epilogue is not None or swiglu) and M > 64:
+        raise KernelError(f"gemm_tc: fused norm / SwiGLU epilogues take at most 64 rows, got {M}")
     if splits is None:
         splits = gemm_tc_splits(M, N, K)
     mode, resid, ldr, norm_w, ss_out = 0, None, 0, None, None

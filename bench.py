@@ -8,7 +8,7 @@ timed steps end at context 4,096).  ``value`` is decoded tokens per second timed
 device with CUDA events (token ids prepared beforehand, sampling kernel included);
 ``e2e`` is the same through ``Engine.step()``: host token ids in, sampled ids out, every
 step.  ``prefill`` is one 2,048-token prompt in one step; ``points`` are decode at batch
-1 and 64; ``roofline`` compares the bytes a decode step must read (every weight once,
+1 and 64 (and all three batches again at context 3,072, the middle of the generation); ``roofline`` compares the bytes a decode step must read (every weight once,
 the cache of the live requests) with the measured copy bandwidth.  Weights are random
 (seeded N(0, 0.02), norms 1), token ids uniform random: synthetic data.  Weights
 (15 GB) are far larger than L2, so no L2 flush is needed between steps.
@@ -339,6 +339,10 @@ def main() -> int:
     if not args.skip_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(time_decode(runner, sampler, b, args.steps, args.warmup, CONTEXT, torch)["tok_s"], 1)
+        # the same three batches in the middle of the generation (context 3,072: prompt 2,048 + 1,024 generated)
+        mid = PROMPT + (CONTEXT - PROMPT) // 2 + (args.steps + args.warmup) // 2
+        for b in (1, 8, 64):
+            points[f"decode_b{b}_ctx3072"] = round(time_decode(runner, sampler, b, args.steps, args.warmup, mid, torch)["tok_s"], 1)
     pre_ms = time_prefill(runner, PROMPT, 3, torch)
     e2e = time_e2e(runner, args.batch, args.steps, args.warmup, CONTEXT, torch)
 
