@@ -79,14 +79,18 @@ class CacheManager:
         self.state_needs = dict(state_needs)
         self.state: dict[int, object] = {}
         self.live: dict[object, RequestCache] = {}
+        # One page per group and one slot beyond the pools, never handed out: rows that only pad a
+        # step to a captured shape write their keys, values and state there.
+        self.pad_page = num_pages
+        self.pad_slot = num_slots
         if allocate:
             import torch
             for g in self.groups:
                 n = g.needs
-                g.storage = torch.zeros((len(g.entries), 2, num_pages, n.num_kv_heads, page_size, n.head_dim),
+                g.storage = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                         dtype=dtype, device=device)
             for entry, sn in self.state_needs.items():
-                self.state[entry] = torch.zeros((num_slots, *sn.shape), dtype=torch.float32, device=device)
+                self.state[entry] = torch.zeros((num_slots + 1, *sn.shape), dtype=torch.float32, device=device)
 
     # ------------------------------------------------------------------ storage views
 

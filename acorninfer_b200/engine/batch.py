@@ -160,6 +160,43 @@ def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
                     as_tiles(tiles), np.asarray(singles, np.int32), as_tiles(large), as_tiles(small))
 
 
+# Row counts that all-decode steps are padded to, so that few shapes are captured as CUDA graphs.
+DECODE_BUCKETS = (1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16, 20, 24, 28, 32, 40, 48, 56, 64, 80, 96, 112, 128)
+
+
+def decode_bucket(n: int) -> int:
+    for b in DECODE_BUCKETS:
+        if n <= b:
+            return b
+    return -(-n // 32) * 32
+
+
+def pad_decode_plan(plan: StepPlan, pad_page: int, pad_slot: int) -> StepPlan:
+    """An all-decode plan padded to its bucket: the added rows feed token 0 at position 0 of a
+    request that exists only as the manager's padding page and slot; the added wanted places point
+    at them.  Callers use the first ``plan.num_rows`` / ``plan.num_logits`` results only."""
+    R, W = plan.num_rows, plan.num_logits
+    Rb, Wb = decode_bucket(R), decode_bucket(W) if W else 0
+    if Rb == R and Wb == W:
+        return plan
+    extra = Rb - R
+    i32 = np.int32
+    cat = lambda a, fill, n: np.concatenate([a, np.full(n, fill, i32)])
+    groups = []
+    for g in plan.groups:
+        bt = np.zeros((Rb, g.block_table.shape[1]), i32)
+        bt[:R] = g.block_table
+        bt[R:, 0] = pad_page
+        groups.append(GroupPlan(cat(g.kv_len, 1, extra), cat(g.page_base, 0, extra), bt, g.max_kv_len))
+    pad_target = R if extra else 0                     # a padding row if there is one, else any row
+    return StepPlan(
+        Rb, Rb, cat(plan.token_ids, 0, extra), cat(plan.positions, 0, extra),
+        np.arange(Rb, dtype=i32), np.arange(Rb + 1, dtype=i32), cat(plan.row_pos, 0, extra),
+        cat(plan.row_slot, pad_slot, extra), cat(plan.logit_tokens, pad_target, Wb - W), groups,
+        plan.row_lens + [1] * extra, 1, True, plan.q_tiles, np.arange(Rb, dtype=i32), plan.q_tiles_large,
+        plan.q_tiles_small)
+
+
 # --------------------------------------------------------------------------- device side
 
 

@@ -30,7 +30,7 @@ from ..models.decoder import Decoder
 from ..registry import load_config, spec_for
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_state
-from .batch import BatchError, StepEntry, StepWorkspace, plan_step, validate_entries
+from .batch import BatchError, StepEntry, StepWorkspace, pad_decode_plan, plan_step, validate_entries
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -120,11 +120,14 @@ class ModelRunner:
         self.reserve(entries)
         plan = plan_step(entries, self.manager)
         self.last_plan = plan
-        inputs = self.workspace.upload(plan)
         if self.decode_graph and plan.all_decode:
-            logits = self._decode_step(plan, inputs)
+            # padded to a bucket of row counts, so that a few captured graphs serve every batch size
+            padded = pad_decode_plan(plan, self.manager.pad_page, self.manager.pad_slot)
+            logits = self._decode_step(padded, self.workspace.upload(padded))
+            if logits is not None and padded.num_logits != plan.num_logits:
+                logits = logits[:plan.num_logits]
         else:
-            logits = self.decoder.forward(inputs, self.caches)
+            logits = self.decoder.forward(self.workspace.upload(plan), self.caches)
         for e in entries:
             self.manager.commit(e.cache, e.cache.length + len(e.tokens))
         return logits

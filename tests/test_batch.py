@@ -97,3 +97,35 @@ def test_request_token_slices():
     for start in range(7):
         for length in range(1, 8 - start):
             assert r.tokens(start, length) == r.all_ids[start:start + length]
+
+
+def test_decode_steps_are_padded_to_buckets_with_rows_that_touch_only_the_padding_page():
+    from acorninfer_b200.engine.batch import decode_bucket, pad_decode_plan
+    assert [decode_bucket(n) for n in (1, 8, 9, 17, 33, 64, 65, 129, 200)] == [1, 8, 10, 20, 40, 64, 80, 160, 224]
+    m = CacheManager({0: KVNeeds(2, 16, None)}, {}, 64, 4, 16, dtype=torch.float32, device="cpu", allocate=False)
+    rcs = [m.open(i) for i in range(5)]
+    entries = []
+    for i, rc in enumerate(rcs):
+        m.extend(rc, 6 + i)
+        m.commit(rc, 5 + i)
+        entries.append(StepEntry(rc, [i + 1], [0] if i != 2 else []))
+    plan = plan_step(entries, m)
+    padded = pad_decode_plan(plan, m.pad_page, m.pad_slot)
+    assert (plan.num_rows, plan.num_logits) == (5, 4) and (padded.num_rows, padded.num_logits) == (5, 4)
+    entries.append(StepEntry(m.open(9), [7], [0]))
+    m.extend(entries[-1].cache, 1)
+    plan = plan_step(entries, m)                       # 6 rows, 5 wanted -> buckets 6 and 5; force a larger case
+    for k in range(3):
+        rc = m.open(20 + k)
+        m.extend(rc, 1)
+        entries.append(StepEntry(rc, [3], [0]))
+    plan = plan_step(entries, m)                       # 9 rows -> 10, 8 wanted -> 8
+    padded = pad_decode_plan(plan, m.pad_page, m.pad_slot)
+    assert padded.num_rows == padded.num_tokens == 10 and padded.num_logits == 8 and padded.all_decode
+    assert padded.token_ids[:9].tolist() == plan.token_ids.tolist() and padded.token_ids[9] == 0
+    assert padded.positions[9] == 0 and padded.row_slot[9] == m.pad_slot == 16 and padded.row_pos[9] == 0
+    g = padded.groups[0]
+    assert g.block_table[9, 0] == m.pad_page == 64 and g.kv_len[9] == 1
+    assert g.block_table[:9].tolist() == plan.groups[0].block_table.tolist()
+    assert padded.row_start.tolist() == list(range(11)) and padded.single_tokens.tolist() == list(range(10))
+    assert m.free_pages()[0] + sum(len(rc.tables[0]) for rc in m.live.values()) == 64   # the padding page is outside the pool
