@@ -39,10 +39,10 @@ class ModelRunner:
     def __init__(self, config: ModelConfig, tensors: dict[str, torch.Tensor] | None, *, dtype: str = "bfloat16",
                  device: str = "cuda:0", num_blocks: int = 1024, page_size: int = 16, max_requests: int = 64,
                  max_step_tokens: int = 8192, decoder: Decoder | None = None, decode_graph: bool = True):
-        ops.lib()      # fails here, loudly, if there is no device or no compiled kernels
         self.config = config
         self.dtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
         self.device = torch.device(device)
+        ops.lib()      # fails here, loudly, if there is no device or no compiled kernels
         torch.cuda.set_device(self.device)
         self.spec = spec_for(config)
         self.decoder = decoder or Decoder(self.spec, self.dtype, self.device, page_size)

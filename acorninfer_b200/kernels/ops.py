@@ -85,7 +85,17 @@ class _Sigs:
     acorn_uniform = [ctypes.c_uint64, ctypes.c_uint64]
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index = None
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle (also the capture stream while a graph is captured)."""
+    global _device_index
+    if _raw_stream is not None:
+        if _device_index is None:
+            _device_index = torch.cuda.current_device()      # the engine works on one device
+        return _raw_stream(_device_index)
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -1,0 +1,55 @@
+"""Captured, padded all-decode steps give the same logits as plain launches of the same steps;
+and the reference-style benchmark module runs on a tiny random model."""
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from tests.tiny import TINY_B, TINY_D, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("tiny", [TINY_B, TINY_D], ids=["tiny_b", "tiny_d"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_with_padding_equals_plain_launches(tmp_path, tiny, dtype):
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.engine.runner import ModelRunner
+
+    d = make_model_dir(tmp_path / "m", tiny)
+    V = tiny["cfg"].vocab_size
+    results = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=64, page_size=tiny["page_size"], max_requests=8,
+                                            decode_graph=graphs)
+        reqs = [runner.open(i) for i in range(5)]
+        for i, rc in enumerate(reqs):                       # prompts of different lengths
+            runner.step([StepEntry(rc, random_tokens(3 + 4 * i, V, i), [])])
+        outs = []
+        for step in range(8):                               # 5 rows (bucket 5), then 3 rows, wanting 2 of them
+            live = reqs if step < 4 else reqs[:3]
+            want = (lambda i: [0]) if step < 4 else (lambda i: [0] if i != 1 else [])
+            logits = runner.step([StepEntry(rc, [(7 * step + i) % V], want(i)) for i, rc in enumerate(live)])
+            outs.append(logits.float().cpu().numpy().copy())
+        if graphs:
+            assert runner.graph_replays >= 4               # the repeated shapes were replayed
+        results[graphs] = outs
+        for rc in reqs:
+            runner.close(rc)
+        runner.manager.assert_balanced()
+    tol = 1e-6 if dtype == "float32" else 2e-2
+    for a, b in zip(results[False], results[True]):
+        assert a.shape == b.shape and np.abs(a - b).max() <= tol
+
+
+def test_bench_module_runs(tmp_path, capsys):
+    from acorninfer_b200.bench import main
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(TINY_B["cfg"].to_dict()))
+    rc = main(["--random-config", str(cfg), "--num-blocks", "64", "--page-size", "8", "--max-running", "4",
+               "--watermark-blocks", "2", "--in-tokens", "12", "--out-tokens", "5", "--concurrency", "1", "3",
+               "--chunked-budget", "16"])
+    out = capsys.readouterr().out
+    assert rc == 0 and out.count("RESULT C=") == 2 and "tok_s=" in out
