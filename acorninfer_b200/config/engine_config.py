@@ -27,7 +27,6 @@ class EngineConfig:
     chunked_budget: int | None = None
     max_step_tokens: int = 8192      # capacity of the step workspace (tokens in one step)
     decode_graph: bool = True        # replay captured CUDA graphs for all-decode steps
-    seed: int = 0
 
     def __post_init__(self) -> None:
         if self.dtype not in DTYPE_NAMES:

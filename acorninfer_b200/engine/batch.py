@@ -227,7 +227,6 @@ class StepInputs:
     single_tokens: object = None
     q_tiles_large: object = None
     q_tiles_small: object = None
-    scratch: dict = field(default_factory=dict)     # per-step products shared by parts (e.g. split plans)
 
     @property
     def num_logits(self) -> int:

@@ -56,7 +56,7 @@ class Engine:
     def from_config(cls, cfg: EngineConfig) -> "Engine":
         runner = ModelRunner.from_model_dir(
             cfg.model_dir, dtype=cfg.dtype, device=cfg.device, num_blocks=cfg.num_blocks, page_size=cfg.page_size,
-            max_requests=cfg.max_running, max_step_tokens=cfg.max_step_tokens)
+            max_requests=cfg.max_running, max_step_tokens=cfg.max_step_tokens, decode_graph=cfg.decode_graph)
         return cls(runner, max_running=cfg.max_running, watermark_blocks=cfg.watermark_blocks,
                    chunked_budget=cfg.chunked_budget)
 

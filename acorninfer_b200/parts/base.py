@@ -83,7 +83,6 @@ class ModelSpec:
     final_norm: PartSpec
     head: str | None                    # tensor name of the output matrix; None: tied to embedding
     positions: dict[str, PartSpec] = field(default_factory=dict)   # shared position encodings by name
-    head_optional_tie: bool = False     # head tensor may be absent: then it is the embedding
 
 
 @dataclass

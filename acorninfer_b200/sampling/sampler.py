@@ -51,7 +51,3 @@ class Sampler:
         if any(t < 0 for t in toks):
             raise ValueError("logits contain NaN or infinity: the model's forward pass is broken")
         return toks, (logprobs.tolist() if want_logprobs else None)
-
-    def greedy(self, logits: torch.Tensor) -> list[int]:
-        R = logits.shape[0]
-        return self.sample(logits, [SamplingParams(temperature=0.0)] * R, [0] * R)[0]
