@@ -72,3 +72,26 @@ def test_mixed_trace_reuses_pages(tiny_case):
     tiny, _, reqs, _ = tiny_case
     steps = traces.mixed(reqs)
     assert traces.max_live_tokens(steps) < sum(-(-len(t) // 64) * 64 for t in reqs.values())
+
+
+def test_weights_stored_in_float32_stay_float32_under_a_bfloat16_engine(tmp_path):
+    """A folder whose tensors are stored in 32 bits: the bfloat16 engine keeps them so and multiplies
+    those matrices in float32 (activations between the parts are still bfloat16)."""
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.replay import TraceSession
+    from acorninfer_b200.weights.random_init import write_random_model
+    from tests.tiny import TINY_A
+
+    tiny = TINY_A
+    d = write_random_model(tmp_path / "m32", tiny["cfg"], tiny["seed"], tiny["sigma"], tiny["sigma_norm"], torch.float32)
+    w = read_weights(d)
+    assert all(t.dtype == torch.float32 for t in w.values())
+    reqs = {"a": random_tokens(45, tiny["cfg"].vocab_size, 1), "b": random_tokens(38, tiny["cfg"].vocab_size, 2)}
+    ref = {rid: plain.forward(sizes_of(tiny["cfg"]), w, toks).numpy() for rid, toks in reqs.items()}
+    steps = traces.decode_tail(reqs)
+    runner = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=-(-traces.max_live_tokens(steps) // 4),
+                                        page_size=4, max_requests=2)
+    assert runner.decoder.embedding.dtype == torch.float32 and runner.decoder.blocks[0].mixer.w_qkv.dtype == torch.float32
+    got = traces.collect(TraceSession(runner).step, steps)
+    for (rid, pos), row in got.items():
+        assert np.abs(row - ref[rid][pos]).max() < 2e-2, (rid, pos)
