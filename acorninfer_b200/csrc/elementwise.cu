@@ -21,6 +21,23 @@ extern "C" int acorn_embed(const int* ids, const void* table, float* out32, int 
     return ACORN_ERR_UNSUPPORTED;
 }
 
+// token_ids[dst[i]] = src_tokens[src[i]]: the ids a step decodes from are the ids the step before it
+// sampled, taken on the device (the host reads them one step later).
+__global__ void patch_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ dst,
+                                    const int* __restrict__ src, const int* __restrict__ src_tokens, int n) {
+    pdl_wait();
+    pdl_trigger();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) token_ids[dst[i]] = src_tokens[src[i]];
+}
+
+extern "C" int acorn_patch_tokens(int* token_ids, const int* dst, const int* src, const int* src_tokens, int n,
+                                  cudaStream_t stream) {
+    if (n <= 0) return 0;
+    return acorn_launch(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, token_ids, dst, src,
+                        src_tokens, n);
+}
+
 // ---------------------------------------------------------------- add + RMSNorm
 // v = resid32[row] (+ delta[row]);  if write_resid: resid32[row] = v
 // out[r] = v * rsqrt(mean(v^2) + eps) * w          (all in float32, one rounding)

@@ -31,6 +31,9 @@ class StepEntry:
     cache: RequestCache
     tokens: list[int]
     want: list[int] = field(default_factory=list)
+    # A single decoded token whose id is still on the device: its index among the tokens the step
+    # before sampled (``tokens`` then holds a placeholder).  See ``ModelRunner.step``.
+    from_device: int | None = None
 
 
 @dataclass
@@ -63,6 +66,8 @@ class StepPlan:
     single_tokens: np.ndarray = None   # flat indices of the tokens of single-token rows (decoded tokens)
     q_tiles_large: np.ndarray = None   # the same rows cut for kernels with TILE_LARGE queries a tile:
     q_tiles_small: np.ndarray = None   # rows of at least LARGE_MIN tokens in large tiles, shorter ones in Q_TILE tiles
+    patch_dst: np.ndarray = None       # flat token indices whose ids come from the device ...
+    patch_src: np.ndarray = None       # ... and where among the previous step's sampled tokens they are
 
     @property
     def num_logits(self) -> int:
@@ -96,6 +101,8 @@ def validate_entries(entries: list[StepEntry], vocab_size: int, max_tokens: int 
         seen.add(id(e.cache))
         if len(e.tokens) < 1:
             raise BatchError(f"request {rid!r} brings no tokens")
+        if e.from_device is not None and len(e.tokens) != 1:
+            raise BatchError(f"request {rid!r}: only a single decoded token can take its id from the device")
         if min(e.tokens) < 0 or max(e.tokens) >= vocab_size:
             bad = next(t for t in e.tokens if not (0 <= int(t) < vocab_size))
             raise BatchError(f"request {rid!r}: token id {bad} outside the vocabulary (0..{vocab_size - 1})")
@@ -155,9 +162,11 @@ def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
     large = [(r, q0) for r, n in enumerate(lens) if n >= LARGE_MIN for q0 in range(0, n, TILE_LARGE)]
     small = [(r, q0) for r, n in enumerate(lens) if 1 < n < LARGE_MIN for q0 in range(0, n, Q_TILE)]
     as_tiles = lambda t: np.asarray(t, np.int32).reshape(-1, 2)
+    patch = [(int(row_start[r]), e.from_device) for r, e in enumerate(entries) if e.from_device is not None]
     return StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
                     np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens),
-                    as_tiles(tiles), np.asarray(singles, np.int32), as_tiles(large), as_tiles(small))
+                    as_tiles(tiles), np.asarray(singles, np.int32), as_tiles(large), as_tiles(small),
+                    np.asarray([p[0] for p in patch], np.int32), np.asarray([p[1] for p in patch], np.int32))
 
 
 # Row counts that all-decode steps are padded to, so that few shapes are captured as CUDA graphs.
@@ -194,7 +203,7 @@ def pad_decode_plan(plan: StepPlan, pad_page: int, pad_slot: int) -> StepPlan:
         np.arange(Rb, dtype=i32), np.arange(Rb + 1, dtype=i32), cat(plan.row_pos, 0, extra),
         cat(plan.row_slot, pad_slot, extra), cat(plan.logit_tokens, pad_target, Wb - W), groups,
         plan.row_lens + [1] * extra, 1, True, plan.q_tiles, np.arange(Rb, dtype=i32), plan.q_tiles_large,
-        plan.q_tiles_small)
+        plan.q_tiles_small, plan.patch_dst, plan.patch_src)
 
 
 # --------------------------------------------------------------------------- device side
@@ -227,6 +236,8 @@ class StepInputs:
     single_tokens: object = None
     q_tiles_large: object = None
     q_tiles_small: object = None
+    patch_dst: object = None
+    patch_src: object = None
 
     @property
     def num_logits(self) -> int:
@@ -274,6 +285,8 @@ class StepWorkspace:
         put("single_tokens", plan.single_tokens.size)
         put("q_tiles_large", plan.q_tiles_large.size)
         put("q_tiles_small", plan.q_tiles_small.size)
+        put("patch_dst", plan.patch_dst.size)
+        put("patch_src", plan.patch_src.size)
         for i, g in enumerate(plan.groups):
             put(f"g{i}.kv_len", R)
             put(f"g{i}.page_base", R)
@@ -295,7 +308,7 @@ class StepWorkspace:
             "row_start": plan.row_start, "row_pos": plan.row_pos, "row_slot": plan.row_slot,
             "logit_tokens": plan.logit_tokens, "q_tiles": plan.q_tiles.reshape(-1),
             "single_tokens": plan.single_tokens, "q_tiles_large": plan.q_tiles_large.reshape(-1),
-            "q_tiles_small": plan.q_tiles_small.reshape(-1),
+            "q_tiles_small": plan.q_tiles_small.reshape(-1), "patch_dst": plan.patch_dst, "patch_src": plan.patch_src,
         }
         for gi, g in enumerate(plan.groups):
             arrays[f"g{gi}.kv_len"] = g.kv_len
@@ -320,4 +333,4 @@ class StepWorkspace:
         return StepInputs(plan.num_tokens, plan.num_rows, view("token_ids"), view("positions"), view("token_row"),
                           view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan,
                           view("q_tiles").view(-1, 2), view("single_tokens"), view("q_tiles_large").view(-1, 2),
-                          view("q_tiles_small").view(-1, 2))
+                          view("q_tiles_small").view(-1, 2), view("patch_dst"), view("patch_src"))

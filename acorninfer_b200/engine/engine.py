@@ -29,6 +29,14 @@ from .scheduler import Scheduler
 
 
 @dataclass
+class _Inflight:
+    """A launched step whose sampled ids the host has not read: who sampled, and the ids on the device."""
+
+    samplers: list
+    sampled: object
+
+
+@dataclass
 class TokenOutput:
     seq_id: int
     token_id: int
@@ -38,7 +46,7 @@ class TokenOutput:
 
 class Engine:
     def __init__(self, runner: ModelRunner, *, max_running: int = 8, watermark_blocks: int = 8,
-                 chunked_budget: int | None = None, default_eos_ids=None):
+                 chunked_budget: int | None = None, default_eos_ids=None, lookahead: bool = True):
         self.runner = runner
         self.manager = runner.manager
         if any(watermark_blocks >= t for t in self.manager.total_pages()):
@@ -49,6 +57,8 @@ class Engine:
         cfg_eos = getattr(runner.config, "eos_token_id", ())
         self.default_eos_ids = frozenset(default_eos_ids if default_eos_ids is not None else cfg_eos)
         self.seqs: dict[int, Request] = {}
+        self.lookahead = lookahead
+        self._inflight: _Inflight | None = None
         self._next_id = 0
         self.steps = 0
 
@@ -101,7 +111,7 @@ class Engine:
         self.scheduler.retire(req)
 
     def has_pending(self) -> bool:
-        return self.scheduler.has_pending()
+        return self.scheduler.has_pending() or self._inflight is not None
 
     def assert_balanced(self) -> None:
         self.manager.assert_balanced()
@@ -109,10 +119,21 @@ class Engine:
     # ------------------------------------------------------------------ the step
 
     def step(self) -> list[TokenOutput]:
+        """Schedules and launches the next step, then returns the tokens of the step before it.
+
+        With ``lookahead`` (the default) the ids a step sampled stay on the device and feed the next
+        step directly; the host reads them only after that next step has been launched, so its
+        bookkeeping overlaps the GPU's work and outputs arrive one call later.  What follows from
+        not knowing the last tokens when scheduling: a request that ends on an eos id has one more
+        row in the step already launched (its result is dropped); requests that end by length are
+        not scheduled again.  Without lookahead every call returns its own step's tokens."""
         outputs: list[TokenOutput] = []
         decision = self.scheduler.schedule()
-        if not decision.portions:
-            if self.scheduler.waiting and not self.scheduler.running:
+        launched = None
+        try:
+            if decision.portions:
+                launched = self._launch(decision)
+            elif self._inflight is None and self.scheduler.waiting and not self.scheduler.running:
                 req = self.scheduler.waiting[0]
                 need = self.manager.peak_pages(req.num_tokens, self.scheduler.chunked_budget)
                 if any(n > t - self.scheduler.watermark for n, t in zip(need, self.manager.total_pages())):
@@ -121,27 +142,54 @@ class Engine:
                     self._finish(req, "capacity")
                     last = req.generated_ids[-1] if req.generated_ids else -1
                     outputs.append(TokenOutput(req.seq_id, last, True, "capacity"))
-            return outputs
-        try:
-            entries, samplers = [], []
-            for p in decision.portions:
-                ids = p.request.tokens(p.start, p.length)
-                entries.append(StepEntry(p.request.cache, ids, [p.length - 1] if p.samples else []))
-                if p.samples:
-                    samplers.append(p.request)
-            logits = self.runner.step(entries)
-            for p in decision.portions:
-                p.request.cursor = p.start + p.length
-            if samplers:
-                tokens, _ = self.sampler.sample(logits, [r.sampling for r in samplers],
-                                                [len(r.generated_ids) for r in samplers])
-                for req, tok in zip(samplers, tokens):
-                    self._record(req, tok, outputs)
+            if self.lookahead:
+                previous, self._inflight = self._inflight, launched
+            else:
+                previous = launched
+            if previous is not None:
+                self._collect(previous, outputs)
         finally:
             for req in [r for r in self.scheduler.running if r.is_finished]:
                 self.scheduler.retire(req)
         self.steps += 1
         return outputs
+
+    def _launch(self, decision) -> "_Inflight | None":
+        """Feeds the scheduled portions to the step function and launches sampling; nothing is read back."""
+        prev = self._inflight
+        prev_index = {id(r): i for i, r in enumerate(prev.samplers)} if prev is not None else {}
+        entries, samplers = [], []
+        for p in decision.portions:
+            r = p.request
+            from_device = None
+            if r.pending and p.start + p.length == r.num_tokens:
+                # its newest token is still on the device (sampled by the step in flight)
+                if p.length != 1 or id(r) not in prev_index:
+                    raise RuntimeError(f"request {r.seq_id}: a token that the host has not read can only be decoded")
+                ids, from_device = [0], prev_index[id(r)]
+            else:
+                ids = r.tokens(p.start, p.length)
+            entries.append(StepEntry(r.cache, ids, [p.length - 1] if p.samples else [], from_device))
+            if p.samples:
+                samplers.append(r)
+        logits = self.runner.step(entries, prev.sampled.tokens if prev is not None else None)
+        for p in decision.portions:
+            p.request.cursor = p.start + p.length
+        if not samplers:
+            return None
+        sampled = self.sampler.launch_async(logits, [r.sampling for r in samplers],
+                                            [r.num_generated for r in samplers])
+        for r in samplers:
+            r.pending += 1
+        return _Inflight(samplers, sampled)
+
+    def _collect(self, inflight: "_Inflight", outputs: list[TokenOutput]) -> None:
+        """Reads a launched step's sampled ids and records them."""
+        for req, tok in zip(inflight.samplers, inflight.sampled.read()):
+            req.pending -= 1
+            if req.is_finished:
+                continue            # it ended on the token before (eos): this row ran for nothing
+            self._record(req, tok, outputs)
 
     def _finish(self, req: Request, reason: str) -> None:
         req.stop_reason = reason

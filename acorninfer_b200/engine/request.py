@@ -32,6 +32,7 @@ class Request:
     status: RequestStatus = RequestStatus.WAITING
     stop_reason: str | None = None
     cursor: int = 0                      # tokens of all_ids already in the cache
+    pending: int = 0                     # tokens sampled on the device that the host has not read yet (0 or 1)
     cache: object = None                 # RequestCache while running
     preemptions: int = 0
     created_at: float = field(default_factory=time.perf_counter)
@@ -40,7 +41,16 @@ class Request:
 
     @property
     def num_tokens(self) -> int:
-        return len(self.prompt_ids) + len(self.generated_ids)
+        return len(self.prompt_ids) + len(self.generated_ids) + self.pending
+
+    @property
+    def num_generated(self) -> int:
+        return len(self.generated_ids) + self.pending
+
+    @property
+    def exhausted(self) -> bool:
+        """All tokens it may generate are sampled; the last one may still be on its way to the host."""
+        return self.num_generated >= self.max_tokens
 
     @property
     def all_ids(self) -> list[int]:

