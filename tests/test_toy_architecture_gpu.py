@@ -150,3 +150,33 @@ def test_toy_architecture_runs_through_the_same_runner_and_replay(toy, dtype, to
         runner.manager.assert_balanced()
         for (rid, pos), row in got.items():
             assert np.abs(row - ref[rid][pos]).max() < tol, (cut, rid, pos)
+
+
+def test_toy_architecture_through_the_engine_with_a_tight_pool(toy):
+    """The same toy model (state slots, a windowed group beside a full one) under the scheduler:
+    greedy generation with a token budget and so few pages that requests are preempted and
+    recomputed; every generated token is the plain computation's best (float32)."""
+    from acorninfer_b200.engine.engine import Engine
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.sampling.params import SamplingParams
+
+    cfg, d = toy
+    w = read_weights(d)
+    prompts = [random_tokens(n, cfg.vocab_size, 500 + n) for n in (14, 9, 21, 5)]
+    runner = ModelRunner.from_model_dir(d, dtype="float32", num_blocks=9, page_size=8, max_requests=3)
+    eng = Engine(runner, max_running=3, watermark_blocks=0, chunked_budget=10)
+    ids = [eng.submit(p, SamplingParams(temperature=0.0), max_tokens=24, eos_ids=()) for p in prompts]
+    steps = 0
+    while eng.has_pending():
+        eng.step()
+        steps += 1
+        assert steps < 1000
+    assert sum(eng.seqs[i].preemptions for i in ids) >= 1          # the pool was tight enough to preempt
+    for i, p in zip(ids, prompts):
+        out = eng.seqs[i].all_ids
+        assert len(out) == len(p) + 24
+        logits = toy_plain(cfg, w, out[:-1])
+        for j in range(len(p), len(out)):
+            row = logits[j - 1]
+            assert float(row.max() - row[out[j]]) < 1e-5, (i, j)
+    eng.assert_balanced()
