@@ -3,6 +3,7 @@
     python -m acorninfer_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096
     python -m acorninfer_b200.kernels.microbench attn-decode --batch 64 --context 4096
     python -m acorninfer_b200.kernels.microbench attn-prefill --tokens 2048
+    python -m acorninfer_b200.kernels.microbench step --layers 8 --batch 8
 
 Prints the time per call and the achieved GB/s (bytes the kernel must read) or TFLOPS.
 Inputs are larger than L2 or rotated over several copies, so DRAM figures mean something;
@@ -107,6 +108,56 @@ def bench_attn_prefill(a) -> None:
     print(f"attention_prefill[{a.kernel}] tokens={T} heads={nq}/{nkv} d={d} page={P}: {us:.1f} us, {fl / us / 1e6:.0f} TFLOPS (causal)")
 
 
+def bench_step(a) -> None:
+    """What each kernel of one decode step adds to the step's end time (kernels overlap under
+    programmatic dependent launch, so the sum of durations would count time twice), from the torch
+    profiler's kernel records of a replayed step on a model of Qwen3-8B layer sizes."""
+    import collections
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..config.model_config import Qwen3Config
+    from ..engine.batch import StepEntry
+    from ..engine.runner import ModelRunner
+
+    cfg = Qwen3Config(num_hidden_layers=a.layers, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                      head_dim=128, intermediate_size=12288, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=151936)
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", num_blocks=a.batch * a.context // 16 + 64,
+                                     page_size=16, max_requests=a.batch + 1)
+    for g in runner.manager.groups:
+        g.storage.normal_(0, 1)
+    reqs = []
+    for i in range(a.batch):
+        rc = runner.open(i)
+        runner.manager.extend(rc, a.context - 16)
+        runner.manager.commit(rc, a.context - 16)
+        reqs.append(rc)
+    one = lambda: runner.step([StepEntry(rc, [5], [0]) for rc in reqs])
+    for _ in range(5):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(2):
+            one()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "emcpy" not in e.name]
+    evs.sort(key=lambda e: e.time_range.start)
+    starts = [i for i, e in enumerate(evs) if "embed_kernel" in e.name]
+    evs = sorted(evs[starts[-1]:], key=lambda e: e.time_range.end)
+    prev = evs[0].time_range.start
+    t0 = prev
+    agg = collections.OrderedDict()
+    for e in evs:
+        name = e.name.split("(")[0].split("<")[0].replace("void ", "")[-44:]
+        entry = agg.setdefault(name, [0, 0.0])
+        entry[0] += 1
+        entry[1] += e.time_range.end - prev
+        prev = e.time_range.end
+    print(f"decode step, batch {a.batch}, context {a.context}, {a.layers} layers: {prev - t0:.1f} us, {len(evs)} kernels")
+    for name, (n, total) in agg.items():
+        print(f"  {name:46s} n={n:4d}  adds {total / n:7.2f} us a call  ({total:8.1f} us in all)")
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="microbench")
     sub = p.add_subparsers(dest="what", required=True)
@@ -132,8 +183,13 @@ def main(argv=None) -> int:
         s.add_argument("--tokens", type=int, default=2048)
         s.add_argument("--splits", type=int, default=0)
         s.add_argument("--kernel", default="mma", choices=["mma", "tc"], help="prefill: mma.sync or tcgen05 kernel")
+    st = sub.add_parser("step", help="per-kernel contributions to one decode step (torch profiler)")
+    st.add_argument("--layers", type=int, default=8)
+    st.add_argument("--batch", type=int, default=8)
+    st.add_argument("--context", type=int, default=4096)
     a = p.parse_args(argv)
-    {"gemm": bench_gemm, "attn-decode": bench_attn_decode, "attn-prefill": bench_attn_prefill}[a.what](a)
+    {"gemm": bench_gemm, "attn-decode": bench_attn_decode, "attn-prefill": bench_attn_prefill,
+     "step": bench_step}[a.what](a)
     return 0
 
 
