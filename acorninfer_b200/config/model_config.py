@@ -17,7 +17,7 @@ from __future__ import annotations
 import json
 from dataclasses import asdict, dataclass, field, fields
 from pathlib import Path
-from typing import Any, ClassVar
+from typing import ClassVar
 
 
 class ConfigError(ValueError):

@@ -10,7 +10,6 @@ reference's own model (imported on the CPU) that this file is checked against on
 
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -1,6 +1,5 @@
 """The step's host-side layout: validation before anything runs, and the arrays the kernels read."""
 
-import numpy as np
 import pytest
 import torch
 

@@ -4,7 +4,6 @@ a token budget, and what happens when pages run out (preemption and recomputatio
 the same tokens; a request that can never fit is stopped)."""
 
 import pytest
-import torch
 
 from tests.plain import model as plain
 from tests.tiny import TINY_A, TINY_B, TINY_C, make_model_dir, random_tokens, read_weights, sizes_of

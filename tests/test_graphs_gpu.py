@@ -5,7 +5,6 @@ import json
 
 import numpy as np
 import pytest
-import torch
 
 from tests.tiny import TINY_B, TINY_D, make_model_dir, random_tokens
 

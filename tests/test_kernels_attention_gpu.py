@@ -5,7 +5,7 @@ edge decides the result."""
 import pytest
 import torch
 
-from tests.paged import gather_from_pages, rows_layout, scatter_to_pages
+from tests.paged import rows_layout, scatter_to_pages
 from tests.plain import model as plain
 
 pytestmark = pytest.mark.gpu

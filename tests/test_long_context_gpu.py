@@ -4,9 +4,7 @@ others at decode time (a fault in a split, a page or a tile far from the query w
 
 import numpy as np
 import pytest
-import torch
 
-from tests import traces
 from tests.plain import model as plain
 from tests.tiny import TINY_D, make_model_dir, random_tokens, read_weights, sizes_of
 
