@@ -120,12 +120,14 @@ def _check(t: torch.Tensor, name: str, dtype=None, dims: int | None = None) -> N
 
 
 LAUNCHES = 0      # kernels of this library launched so far (for reports)
+COUNTS: dict[str, int] = {}    # the same by entry point: tests use it to see which kernel a path really took
 
 
 def _ok(code: int, what: str) -> None:
     global LAUNCHES
     if code == 0:
         LAUNCHES += 1
+        COUNTS[what] = COUNTS.get(what, 0) + 1
         return
     if code == 10001:
         raise KernelError(f"{what}: sizes or dtypes not supported by this kernel")
