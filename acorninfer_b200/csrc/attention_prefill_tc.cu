@@ -3,21 +3,27 @@
 // values in the paged cache, S = Q K^T and O += P V computed by tcgen05.mma with the accumulators
 // in tensor memory, K/V/Q tiles brought by TMA through the block table.
 //
-// One CTA per (tile of 128 queries, query head), 6 warps, two CTAs to an SM:
-//   warps 0-3  softmax: thread r owns query row r (= TMEM lane r): reads its row of S with
-//              tcgen05.ld, masks by absolute position (causal, window) where a block needs it,
-//              exponentiates in float32 base 2 against a reference maximum, writes P (bfloat16)
-//              into a swizzled shared-memory tile.  O stays in tensor memory across blocks; it
-//              is rescaled (tcgen05.ld / st) only when a row's maximum has grown by more than
-//              2^8 since its reference was set, so most blocks skip that pass.  At the end the
-//              thread reads its row of O, divides by the row sum and writes the output.
-//   warp 4     producer: TMA loads of Q (once) and, per block of 64 keys, of the K and V page
-//              tiles ((page, kv head) tiles are contiguous [page_size x 128] in the cache).
-//   warp 5     MMA issuer: S[j] = Q K_j^T into one of two S buffers (the next block's scores are
-//              computed while the softmax warps work on this one), then O += P_j V_j.
-// Tensor memory: S0, S1 (64 columns each), O (128 columns).  V is the MN-major B operand of the
-// second product (head dims contiguous); P is a K-major A operand written by the softmax
-// warps (generic proxy) and fenced to the async proxy.
+// One CTA per (tile of 128 queries, pair of query heads that share a key/value head), one CTA to
+// an SM.  The two heads ("units") read the same K/V tiles, which are loaded once, and take turns
+// on the tensor cores: while the softmax warps of both units work on block j, the tensor cores
+// compute the scores of block j+1 and add P V of block j.  With an odd number of query heads per
+// key/value head the last CTA of a group has one unit only.
+//   warps 0-3  softmax of unit 0, warps 4-7 of unit 1: thread r owns query row r (= TMEM lane r):
+//              reads its row of S with tcgen05.ld, masks by absolute position (causal, window)
+//              where a block needs it, exponentiates in float32 base 2 against a reference
+//              maximum, writes P (bfloat16) into a swizzled shared-memory tile.  O stays in tensor
+//              memory across blocks; it is rescaled (tcgen05.ld / st) only when a row's maximum
+//              has grown by more than 2^8 since its reference was set, so most blocks skip that
+//              pass.  At the end the thread reads its row of O, divides by the row sum and writes
+//              the output.
+//   warp 8     producer: TMA loads of Q (once) and, per block of 64 keys, of the K and V page
+//              tiles ((page, kv head) tiles are contiguous [page_size x 128] in the cache) into a
+//              ring of four stages, so that loads run three blocks ahead of the products.
+//   warp 9     MMA issuer: S_u[j+1] = Q_u K_{j+1}^T into one of two S buffers per unit, then
+//              O_u += P_u[j] V_j for both units.
+// Tensor memory (512 columns): S buffers 2 units x 2 x 64 columns, O 2 units x 128 columns.  V is
+// the MN-major B operand of the second product (head dims contiguous); P is a K-major A operand
+// written by the softmax warps (generic proxy) and fenced to the async proxy.
 //
 // Every mbarrier wait is bounded; a wait that gives up records g_attn_tc_error and the CTA
 // drains without touching tensor memory it does not own.
@@ -26,8 +32,8 @@
 #define ATC_D 128
 #define ATC_BM 128
 #define ATC_BN 64
-#define ATC_STAGES 2
-#define ATC_THREADS 192
+#define ATC_STAGES 4            // a power of two
+#define ATC_THREADS 320
 #define ATC_RESCALE_LOG2 8.0f     // rescale O only when the row maximum grew by more than this (base 2)
 
 __device__ int g_attn_tc_error = 0;
@@ -40,37 +46,44 @@ struct AttnTcParams {
     const int* row_pos;
     const int* tiles;        // [n_tiles, 2]: row, first token of the tile within the row
     int table_stride, nq, nkv, logP, window;
+    int n_tiles, pairs;      // pairs = ceil((nq / nkv) / 2): CTAs per (tile, kv head)
     float scale_log2;
 };
 
 // shared memory map (bytes; the tile regions are 1024-aligned)
-#define ATC_Q_BYTES (2 * ATC_BM * 128)                    // two 64-element halves of [128 x 128]
+#define ATC_Q_BYTES (2 * ATC_BM * 128)                    // one unit: two 64-element halves of [128 x 128]
 #define ATC_KV_HALF (ATC_BN * 128)                         // one half of a K or V block: [64 keys x 64 dims]
 #define ATC_STAGE_BYTES (4 * ATC_KV_HALF)                  // K half 0, K half 1, V half 0, V half 1
-#define ATC_P_BYTES (ATC_BM * 128)                         // [128 rows x 64 keys] bf16
-#define ATC_SMEM_TILES (ATC_Q_BYTES + ATC_STAGES * ATC_STAGE_BYTES + ATC_P_BYTES)
-#define ATC_NUM_BARS (1 + 2 * ATC_STAGES + 2 + 1 + 1)      // q_full, kv_full/empty, s_full[2], p_full, o_done
+#define ATC_P_BYTES (ATC_BM * 128)                         // one unit: [128 rows x 64 keys] bf16
+#define ATC_SMEM_TILES (2 * ATC_Q_BYTES + ATC_STAGES * ATC_STAGE_BYTES + 2 * ATC_P_BYTES)
+// q_full, kv_full[STAGES], kv_empty[STAGES], s_full[unit][2], p_full[unit], o_done[unit]
+#define ATC_NUM_BARS (1 + 2 * ATC_STAGES + 4 + 2 + 2)
+#define ATC_TMEM_COLS 512
 
-__global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                               const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v,
                                                                               const AttnTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sKV = sQ + ATC_Q_BYTES;
+    uint8_t* sKV = sQ + 2 * ATC_Q_BYTES;
     uint8_t* sP = sKV + ATC_STAGES * ATC_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + ATC_P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATC_P_BYTES);
     const uint32_t q_full = tc_smem(bars);
-    const uint32_t kv_full0 = tc_smem(bars + 1), kv_empty0 = tc_smem(bars + 1 + ATC_STAGES);
-    const uint32_t s_full0 = tc_smem(bars + 1 + 2 * ATC_STAGES);
-    const uint32_t p_full = s_full0 + 16, o_done = p_full + 8;
+    const uint32_t kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * ATC_STAGES;
+    const uint32_t s_full0 = kv_empty0 + 8 * ATC_STAGES;        // s_full[unit][buffer] at + 16 * unit + 8 * buffer
+    const uint32_t p_full0 = s_full0 + 32, o_done0 = p_full0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + ATC_NUM_BARS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // tiles are listed by rising position within a request; the late tiles read the most keys, so
-    // they are started first
-    const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
-    const int kvh = head / (p.nq / p.nkv);
+    // Tiles are listed by rising position within a request; the late tiles read the most keys, so
+    // they are started first.  CTAs next to one another share a key/value head (and tile).
+    const int per_tile = p.nkv * p.pairs;
+    const int tile = p.n_tiles - 1 - (int)(blockIdx.x / per_tile);
+    const int kvh = (int)(blockIdx.x % per_tile) / p.pairs, pair = (int)(blockIdx.x % per_tile) % p.pairs;
+    const int rep = p.nq / p.nkv;
+    const int head0 = kvh * rep + 2 * pair;
+    const int units = (2 * pair + 1 < rep) ? 2 : 1;
     if (tc_smem(smem) & 1023u) {            // the swizzled tiles need a 1024-byte aligned base
         if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 9);
         return;
@@ -79,21 +92,21 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < ATC_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-        for (int s = 0; s < 2; ++s) mbar_init(s_full0 + 8 * s, 1);
-        mbar_init(p_full, 4);
-        mbar_init(o_done, 1);
+        for (int s = 0; s < 4; ++s) mbar_init(s_full0 + 8 * s, 1);
+        for (int u = 0; u < 2; ++u) { mbar_init(p_full0 + 8 * u, 4); mbar_init(o_done0 + 8 * u, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     :: "r"(tc_smem(tmem_slot)), "r"(256u) : "memory");
+                     :: "r"(tc_smem(tmem_slot)), "r"((uint32_t)ATC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 128;
+    // S of unit u, buffer b: columns u * 128 + b * 64;  O of unit u: columns 256 + u * 128
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;
 
     pdl_wait();
     pdl_trigger();
@@ -107,11 +120,13 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     lo &= ~(ATC_BN - 1);                                                 // blocks start at multiples of 64 keys
     const int nb = (hi - lo + ATC_BN - 1) / ATC_BN;
 
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         // ---------------------------------------------------------------- producer
-        mbar_expect_tx(q_full, ATC_Q_BYTES);
-        tma_load_2d(tc_smem(sQ), &map_q, q_full, head * ATC_D, tok0);
-        tma_load_2d(tc_smem(sQ) + ATC_BM * 128, &map_q, q_full, head * ATC_D + 64, tok0);
+        mbar_expect_tx(q_full, units * ATC_Q_BYTES);
+        for (int u = 0; u < units; ++u) {
+            tma_load_2d(tc_smem(sQ) + u * ATC_Q_BYTES, &map_q, q_full, (head0 + u) * ATC_D, tok0);
+            tma_load_2d(tc_smem(sQ) + u * ATC_Q_BYTES + ATC_BM * 128, &map_q, q_full, (head0 + u) * ATC_D + 64, tok0);
+        }
         const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
         const int P = 1 << p.logP;
         const int rows_per_op = P < ATC_BN ? P : ATC_BN;               // rows one TMA box brings
@@ -136,69 +151,88 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
                 tma_load_2d(base + 3 * ATC_KV_HALF + off, &map_v, kv_full0 + 8 * s, 64, row);
             }
         }
-    } else if (warp == 5 && lane == 0) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
+        // The whole warp runs this loop, so that its counters, addresses and descriptors are
+        // warp-uniform values; one elected lane issues each tcgen05 instruction.
         constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ATC_BN >> 3) << 17) |
                                       ((uint32_t)(ATC_BM >> 4) << 24);
         constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(ATC_D >> 3) << 17) | ((uint32_t)(ATC_BM >> 4) << 24);
-        bool good = mbar_wait(q_full, 0);
-        if (!good) atomicExch(&g_attn_tc_error, 2);
+        auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+            bool ok = mbar_wait(bar, parity);
+            if (!ok && lane == 0) atomicExch(&g_attn_tc_error, code);
+            return __all_sync(0xffffffffu, ok);
+        };
+        bool good = wait_all(q_full, 0, 2);
+        // descriptor low words: Q per unit, first K/V stage, P per unit (see umma_bf16_lo)
+        const uint32_t qlo = umma_lo(tc_smem(sQ)), klo0 = umma_lo(tc_smem(sKV));
+        const uint32_t vlo0 = umma_lo_mn(tc_smem(sKV) + 2 * ATC_KV_HALF, ATC_KV_HALF), plo = umma_lo(tc_smem(sP));
         auto issue_qk = [&](int j) {
-            const int s = j % ATC_STAGES;
-            if (!mbar_wait(kv_full0 + 8 * s, (j / ATC_STAGES) & 1)) { atomicExch(&g_attn_tc_error, 3); good = false; return; }
+            const int s = j & (ATC_STAGES - 1);
+            good = wait_all(kv_full0 + 8 * s, (j / ATC_STAGES) & 1, 3);
+            if (!good) return;
             tc_fence_after();
-            const uint32_t kb = tc_smem(sKV + s * ATC_STAGE_BYTES);
+            const uint32_t klo = klo0 + s * (ATC_STAGE_BYTES >> 4);
+            const uint32_t sc = tmem_s + (j & 1) * ATC_BN;
 #pragma unroll
-            for (int k = 0; k < ATC_D / 16; ++k) {
-                const uint32_t half = k >> 2, kk = k & 3;
-                umma_bf16(tmem_s0 + (j & 1) * ATC_BN, umma_desc(tc_smem(sQ) + half * ATC_BM * 128) + 2 * kk,
-                          umma_desc(kb + half * ATC_KV_HALF) + 2 * kk, IDESC_QK, k > 0 ? 1u : 0u);
+            for (int u = 0; u < 2; ++u) {
+                if (u < units) {
+#pragma unroll
+                    for (int k = 0; k < ATC_D / 16; ++k)
+                        umma_bf16_elect(sc + u * 128, qlo + ((u * ATC_Q_BYTES + (k >> 2) * ATC_BM * 128) >> 4) + 2 * (k & 3),
+                                        klo + (((k >> 2) * ATC_KV_HALF) >> 4) + 2 * (k & 3), IDESC_QK, k > 0 ? 1u : 0u);
+                    umma_commit_elect(s_full0 + 16 * u + 8 * (j & 1));
+                }
             }
-            umma_commit(s_full0 + 8 * (j & 1));
         };
         if (good && nb > 0) issue_qk(0);
         for (int j = 0; j < nb && good; ++j) {
-            // S[(j+1) & 1] is free: the softmax warps read block j-1 from it before they signalled
-            // p_full for j-1.  With two K/V stages the tiles of block j+1 arrive after P V of block
-            // j-1 has completed; the other CTA of the SM computes meanwhile.
+            // S buffer (j+1) & 1 of each unit is free: its softmax warps read block j-1 from it
+            // before they signalled p_full for j-1, which P V of block j-1 waited for.
             if (j + 1 < nb) issue_qk(j + 1);
             if (!good) break;
-            if (!mbar_wait(p_full, j & 1)) { atomicExch(&g_attn_tc_error, 4); break; }
-            tc_fence_after();
-            const int s = j % ATC_STAGES;
-            const uint32_t vb = tc_smem(sKV + s * ATC_STAGE_BYTES) + 2 * ATC_KV_HALF;
-            const uint32_t pb = tc_smem(sP);
+            const int s = j & (ATC_STAGES - 1);
+            const uint32_t vlo = vlo0 + s * (ATC_STAGE_BYTES >> 4);
 #pragma unroll
-            for (int k = 0; k < ATC_BN / 16; ++k)       // 16 keys a step: P advances 32 bytes, V 16 rows of 128 bytes
-                umma_bf16(tmem_o, umma_desc(pb) + 2 * k, umma_desc_mn(vb + k * 16 * 128, ATC_KV_HALF), IDESC_PV,
-                          (j > 0 || k > 0) ? 1u : 0u);
-            umma_commit(kv_empty0 + 8 * s);
-            umma_commit(o_done);
+            for (int u = 0; u < 2; ++u) {
+                if (u < units && good) {
+                    good = wait_all(p_full0 + 8 * u, j & 1, 4);
+                    if (good) {
+                        tc_fence_after();
+                        // 16 keys a step: P advances 32 bytes, V 16 rows of 128 bytes
+                        umma_bf16_elect(tmem_o + u * 128, plo + ((u * ATC_P_BYTES) >> 4), vlo, IDESC_PV, j > 0 ? 1u : 0u);
+#pragma unroll
+                        for (int k = 1; k < ATC_BN / 16; ++k)
+                            umma_bf16_elect(tmem_o + u * 128, plo + ((u * ATC_P_BYTES) >> 4) + 2 * k,
+                                            vlo + ((k * 16 * 128) >> 4), IDESC_PV, 1u);
+                        umma_commit_elect(o_done0 + 8 * u);
+                    }
+                }
+            }
+            if (!good) break;
+            umma_commit_elect(kv_empty0 + 8 * s);       // both units have read the stage
         }
-    } else if (warp < 4) {
+    } else if (warp < 4 * units) {
         // ---------------------------------------------------------------- softmax and output
-        const int row = threadIdx.x;                                     // query row = TMEM lane
+        const int u = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;                          // query row = TMEM lane
+        const int head = head0 + u;
         const int qpos = pos0 + row;
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t my_s = tmem_s + lane_addr + u * 128, my_o = tmem_o + lane_addr + u * 128;
+        const uint32_t s_full = s_full0 + 16 * u, p_full = p_full0 + 8 * u, o_done = o_done0 + 8 * u;
+        uint8_t* prow = sP + u * ATC_P_BYTES + row * 128;
         float m_ref = -INFINITY, l_run = 0.f;
         bool good = true;
         for (int j = 0; j < nb; ++j) {
-            if (good && !mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
+            if (good && !mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
             good = __all_sync(0xffffffffu, good);
             if (!good) break;
             tc_fence_after();
             const int key0 = lo + j * ATC_BN;
             float s[ATC_BN];
-            {
-                float part[32];
-                tmem_ld32(tmem_s0 + lane_addr + (j & 1) * ATC_BN, part);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[i] = part[i];
-                tmem_ld32(tmem_s0 + lane_addr + (j & 1) * ATC_BN + 32, part);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
-            }
+            tmem_ld64(my_s + (j & 1) * ATC_BN, s);
             // a block every query of the tile sees whole needs no mask
             if (key0 + ATC_BN - 1 > pos0 || p.window > 0 || n_q < ATC_BM) {
 #pragma unroll
@@ -208,10 +242,13 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
                     s[c] = okk ? s[c] : -INFINITY;
                 }
             }
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < ATC_BN; ++c) mx = fmaxf(mx, s[c]);
-            mx *= p.scale_log2;                                          // the scale is positive
+            for (int c = 0; c < ATC_BN; c += 4) {
+                mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;   // the scale is positive
             // reference maximum: moved only when the row maximum outgrew it by more than 2^8
             float corr = 1.f;
             if (mx > m_ref + ATC_RESCALE_LOG2) {
@@ -220,17 +257,17 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
                 m_ref = mx;
             }
             const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
-            float psum = 0.f;
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t w[ATC_BN / 2];
 #pragma unroll
             for (int c = 0; c < ATC_BN; c += 2) {
                 const float a = fast_exp2(fmaf(s[c], p.scale_log2, neg_ref));
                 const float b = fast_exp2(fmaf(s[c + 1], p.scale_log2, neg_ref));
-                psum += a + b;
+                ps4[(c >> 1) & 3] += a + b;
                 __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
                 w[c >> 1] = *reinterpret_cast<uint32_t*>(&v);
             }
-            l_run += psum;
+            l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
             // P V of the block before has completed: the P tile is free and O is stable
             if (j > 0) {
                 if (!mbar_wait(o_done, (j - 1) & 1)) { atomicExch(&g_attn_tc_error, 7); good = false; }
@@ -241,14 +278,13 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
 #pragma unroll
                     for (int c = 0; c < ATC_D; c += 32) {
                         float part[32];
-                        tmem_ld32(tmem_o + lane_addr + c, part);
+                        tmem_ld32(my_o + c, part);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) part[i] *= corr;
-                        tmem_st32(tmem_o + lane_addr + c, part);
+                        tmem_st32(my_o + c, part);
                     }
                 }
             }
-            uint8_t* prow = sP + row * 128;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch)                                // 8 chunks of 8 keys (16 bytes), swizzled
                 *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
@@ -269,7 +305,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
 #pragma unroll
             for (int c = 0; c < ATC_D; c += 32) {
                 float part[32];
-                tmem_ld32(tmem_o + lane_addr + c, part);
+                tmem_ld32(my_o + c, part);
                 if (row < n_q) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -287,8 +323,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 2) attention_prefill_tc_kernel(co
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(256u) : "memory");
+    if (warp == 9) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     :: "r"(tmem_base), "r"((uint32_t)ATC_TMEM_COLS) : "memory");
     }
 }
 
@@ -310,6 +347,9 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
     p.out = (bf16*)out; p.block_table = block_table; p.page_base = page_base; p.row_start = row_start;
     p.row_pos = row_pos; p.tiles = tiles; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
     p.logP = acorn_log2_exact_tc(P); p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.n_tiles = n_tiles; p.pairs = (nq / nkv + 1) / 2;
+    const int64_t ctas = (int64_t)n_tiles * nkv * p.pairs;
+    if (ctas > 0x7fffffff) return ACORN_ERR_UNSUPPORTED;
     CUtensorMap mq, mk, mv;
     int rc = make_map(&mq, q, tokens, (int64_t)nq * d, q_stride, 64, ATC_BM);
     if (rc) return rc;
@@ -326,7 +366,7 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return acorn_launch(attention_prefill_tc_kernel, dim3(n_tiles, nq), dim3(ATC_THREADS), smem, stream, mq, mk, mv, p);
+    return acorn_launch(attention_prefill_tc_kernel, dim3((unsigned)ctas), dim3(ATC_THREADS), smem, stream, mq, mk, mv, p);
 }
 
 extern "C" int acorn_attention_tc_error() {

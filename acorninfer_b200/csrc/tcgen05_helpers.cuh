@@ -56,8 +56,83 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
         :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Issuing from a converged warp.  tcgen05.mma and tcgen05.commit are issued by one thread, but
+// the warp that issues them should stay converged, with only the instruction itself under the
+// predicate of elect.sync: then loop counters, addresses and descriptors are warp-uniform values
+// that the instruction takes directly.  Issued from a branch that a single thread runs, each
+// tcgen05.mma cost about 80 clocks here whatever its shape; issued this way it costs what the
+// tensor pipe needs (48 clocks at N = 64, 64 at N = 128, 128 at N = 256 for M = 128, K = 16).
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n .reg .b32 rx;\n .reg .pred px;\n elect.sync rx|px, 0xffffffff;\n @px mov.s32 %0, 1;\n}\n" : "+r"(pred));
+    return pred;
+}
+
+// The high word of a 128-byte-swizzle descriptor is a constant (UMMA_DESC_HI) and the low word is
+// start address / 16 plus the leading offset field, so that stepping through tiles is one 32-bit
+// add per operand.
+#define UMMA_DESC_HI ((uint32_t)((1024u >> 4) | (1u << 14) | (2u << 29)))
+__device__ __forceinline__ uint32_t umma_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFF) | (1u << 16); }
+__device__ __forceinline__ uint32_t umma_lo_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ void umma_bf16_lo(uint32_t tmem_d, uint32_t alo, uint32_t blo, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %4, 0;\n"
+        " mov.b64 da, {%1, %5};\n mov.b64 db, {%2, %5};\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n}\n"
+        :: "r"(tmem_d), "r"(alo), "r"(blo), "r"(idesc), "r"(accumulate), "r"(UMMA_DESC_HI) : "memory");
+}
+// Called by all lanes of a converged warp; one elected lane issues.
+__device__ __forceinline__ void umma_bf16_elect(uint32_t tmem_d, uint32_t alo, uint32_t blo, uint32_t idesc,
+                                                uint32_t accumulate) {
+    if (elect_one()) umma_bf16_lo(tmem_d, alo, blo, idesc, accumulate);
+}
+
+// The A operand read from tensor memory (lanes = rows, 16-bit elements two to a column), B from
+// shared memory; called by all lanes of a converged warp.
+__device__ __forceinline__ void umma_bf16_ts_elect(uint32_t tmem_d, uint32_t tmem_a, uint32_t blo, uint32_t idesc,
+                                                   uint32_t accumulate) {
+    if (elect_one()) {
+        asm volatile(
+            "{\n .reg .pred p;\n .reg .b64 db;\n setp.ne.b32 p, %4, 0;\n"
+            " mov.b64 db, {%2, %5};\n"
+            " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n}\n"
+            :: "r"(tmem_d), "r"(tmem_a), "r"(blo), "r"(idesc), "r"(accumulate), "r"(UMMA_DESC_HI) : "memory");
+    }
+}
+
+// One try of a wait (true when the phase with this parity has completed).  Issued early, its
+// latency overlaps the instructions up to the first use of the result.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred P1;\n mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n selp.u32 %0, 1, 0, P1;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+
+// Stores 32 columns of 32 bits (raw) of this thread's TMEM lane; the caller waits (tcgen05.wait::st).
+__device__ __forceinline__ void tmem_st32_raw(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31,%32};\n"
+        :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+           "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+           "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+           "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+    if (elect_one()) umma_commit(bar);
 }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
@@ -111,6 +186,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 64 consecutive float32 columns of this thread's TMEM lane, one load.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,"
+        "%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // Stores 32 float32 columns of this thread's TMEM lane.

@@ -213,7 +213,7 @@ def test_attention_prefill_kernel(nq, nkv, d, P, window):
 
 
 @pytest.mark.parametrize("nq,nkv,P,window", [(32, 8, 16, None), (4, 4, 8, None), (6, 2, 64, None), (8, 1, 16, 200),
-                                             (2, 1, 128, None)])
+                                             (2, 1, 128, None), (10, 2, 32, 300)])
 def test_attention_prefill_tcgen05_kernel(nq, nkv, P, window):
     """The tcgen05/TMA prefill kernel (head size 128): portions that start inside a request and inside
     a page, tiles that end inside a page, rows shorter than a tile, a far key that decides."""
