@@ -116,20 +116,23 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
             tma_load_2d(a, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
             tma_load_2d(a + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, m0);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer
+    } else if (warp == 1) {
+        // ---- MMA issuer: the whole warp runs the loop (uniform counters and descriptors), one
+        // elected lane issues each tcgen05 instruction
+        const uint32_t alo0 = umma_lo(tc_smem(smem)), blo0 = umma_lo(tc_smem(smem) + A_BYTES);
         for (int i = 0; i < nkb; ++i) {
             const int s = i % STAGES;
-            if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1)) { atomicExch(&g_gemm_tc_error, 2); break; }
+            bool got = mbar_wait(full0 + 8 * s, (i / STAGES) & 1);
+            if (!got && lane == 0) atomicExch(&g_gemm_tc_error, 2);
+            if (!__all_sync(0xffffffffu, got)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a = tc_smem(smem + s * STAGE_BYTES);
-            const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + A_BYTES);
+            const uint32_t alo = alo0 + s * (STAGE_BYTES >> 4), blo = blo0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; ++k)     // 16 elements = 32 bytes = 2 descriptor units along K
-                umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
-            umma_commit(empty0 + 8 * s);             // the stage is free once these MMAs have read it
+                umma_bf16_elect(tmem_base, alo + 2 * k, blo + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit_elect(empty0 + 8 * s);       // the stage is free once these MMAs have read it
         }
-        umma_commit(accum_bar);                      // the accumulator is complete
+        umma_commit_elect(accum_bar);                // the accumulator is complete
     }
     __syncwarp();
 
