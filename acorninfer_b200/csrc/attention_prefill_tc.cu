@@ -5,25 +5,26 @@
 //
 // One CTA per (tile of 128 queries, pair of query heads that share a key/value head), one CTA to
 // an SM.  The two heads ("units") read the same K/V tiles, which are loaded once, and take turns
-// on the tensor cores: while the softmax warps of both units work on block j, the tensor cores
-// compute the scores of block j+1 and add P V of block j.  With an odd number of query heads per
-// key/value head the last CTA of a group has one unit only.
+// on the tensor cores: while the softmax warps of one unit work on a block of 128 keys, the
+// tensor cores add P V of the other unit's block and compute its next scores.  With an odd
+// number of query heads per key/value head the last CTA of a group has one unit only.
 //   warps 0-3  softmax of unit 0, warps 4-7 of unit 1: thread r owns query row r (= TMEM lane r):
 //              reads its row of S with tcgen05.ld, masks by absolute position (causal, window)
 //              where a block needs it, exponentiates in float32 base 2 against a reference
-//              maximum, writes P (bfloat16) into a swizzled shared-memory tile.  O stays in tensor
-//              memory across blocks; it is rescaled (tcgen05.ld / st) only when a row's maximum
-//              has grown by more than 2^8 since its reference was set, so most blocks skip that
-//              pass.  At the end the thread reads its row of O, divides by the row sum and writes
-//              the output.
-//   warp 8     producer: TMA loads of Q (once) and, per block of 64 keys, of the K and V page
-//              tiles ((page, kv head) tiles are contiguous [page_size x 128] in the cache) into a
-//              ring of four stages, so that loads run three blocks ahead of the products.
-//   warp 9     MMA issuer: S_u[j+1] = Q_u K_{j+1}^T into one of two S buffers per unit, then
-//              O_u += P_u[j] V_j for both units.
-// Tensor memory (512 columns): S buffers 2 units x 2 x 64 columns, O 2 units x 128 columns.  V is
-// the MN-major B operand of the second product (head dims contiguous); P is a K-major A operand
-// written by the softmax warps (generic proxy) and fenced to the async proxy.
+//              maximum and writes P (bfloat16, two keys to a column) over the first half of S
+//              with tcgen05.st.  O stays in tensor memory across blocks; it is rescaled
+//              (tcgen05.ld / st) only when a row's maximum has grown by more than 2^8 since its
+//              reference was set, so most blocks skip that pass.  At the end the thread reads
+//              its row of O, divides by the row sum and writes the output.
+//   warp 8     producer: TMA loads of Q (once) and of the K and V tiles of each block
+//              ((page, kv head) tiles are contiguous [page_size x 128] in the cache) into a ring
+//              of five 32 KB slots, K_0 V_0 K_1 V_1 ..., so that loads run two blocks ahead.
+//   warp 9     MMA issuer (converged; one elected lane issues): per block j and unit u,
+//              O_u += P_u[j] V_j with P as the A operand from tensor memory, then
+//              S_u = Q_u K_{j+1}^T into the columns P_u[j] was read from (the tensor pipe runs
+//              the products in the order they were issued).
+// Tensor memory (512 columns): S / P of unit u at columns 128 u, O of unit u at 256 + 128 u.
+// V is the MN-major B operand of the second product (head dims contiguous).
 //
 // Every mbarrier wait is bounded; a wait that gives up records g_attn_tc_error and the CTA
 // drains without touching tensor memory it does not own.
@@ -31,8 +32,8 @@
 
 #define ATC_D 128
 #define ATC_BM 128
-#define ATC_BN 64
-#define ATC_STAGES 4            // a power of two
+#define ATC_BN 128
+#define ATC_SLOTS 5
 #define ATC_THREADS 320
 #define ATC_RESCALE_LOG2 8.0f     // rescale O only when the row maximum grew by more than this (base 2)
 
@@ -52,13 +53,46 @@ struct AttnTcParams {
 
 // shared memory map (bytes; the tile regions are 1024-aligned)
 #define ATC_Q_BYTES (2 * ATC_BM * 128)                    // one unit: two 64-element halves of [128 x 128]
-#define ATC_KV_HALF (ATC_BN * 128)                         // one half of a K or V block: [64 keys x 64 dims]
-#define ATC_STAGE_BYTES (4 * ATC_KV_HALF)                  // K half 0, K half 1, V half 0, V half 1
-#define ATC_P_BYTES (ATC_BM * 128)                         // one unit: [128 rows x 64 keys] bf16
-#define ATC_SMEM_TILES (2 * ATC_Q_BYTES + ATC_STAGES * ATC_STAGE_BYTES + 2 * ATC_P_BYTES)
-// q_full, kv_full[STAGES], kv_empty[STAGES], s_full[unit][2], p_full[unit], o_done[unit]
-#define ATC_NUM_BARS (1 + 2 * ATC_STAGES + 4 + 2 + 2)
+#define ATC_HALF_BYTES (ATC_BN * 128)                      // one half of a K or V tile: [128 keys x 64 dims]
+#define ATC_TILE_BYTES (2 * ATC_HALF_BYTES)
+#define ATC_SMEM_TILES (2 * ATC_Q_BYTES + ATC_SLOTS * ATC_TILE_BYTES)
+// q_full, full[SLOTS], empty[SLOTS], s_full[unit], p_full[unit], o_done[unit]
+#define ATC_NUM_BARS (1 + 2 * ATC_SLOTS + 2 + 2 + 2)
 #define ATC_TMEM_COLS 512
+
+// -inf where the query at qpos may not see the key (causal, window, rows beyond the tile's queries)
+__device__ __forceinline__ void atc_mask(float (&s)[64], int key0, int qpos, bool row_ok, int window) {
+#pragma unroll
+    for (int c = 0; c < 64; ++c) {
+        const int key = key0 + c;
+        const bool okk = key <= qpos && row_ok && (window <= 0 || key > qpos - window);
+        s[c] = okk ? s[c] : -INFINITY;
+    }
+}
+
+__device__ __forceinline__ float atc_max(const float (&s)[64]) {
+    float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int c = 0; c < 64; c += 4) {
+        m[0] = fmaxf(m[0], s[c]); m[1] = fmaxf(m[1], s[c + 1]);
+        m[2] = fmaxf(m[2], s[c + 2]); m[3] = fmaxf(m[3], s[c + 3]);
+    }
+    return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
+
+// w[i] = bf16x2(2^(s[2i] * scale - ref), 2^(s[2i+1] * scale - ref)); returns the sum of the 64 values
+__device__ __forceinline__ float atc_exp_pack(const float (&s)[64], float scale_log2, float neg_ref, uint32_t (&w)[32]) {
+    float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 64; c += 2) {
+        const float a = fast_exp2(fmaf(s[c], scale_log2, neg_ref));
+        const float b = fast_exp2(fmaf(s[c + 1], scale_log2, neg_ref));
+        ps[(c >> 1) & 3] += a + b;
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        w[c >> 1] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    return (ps[0] + ps[1]) + (ps[2] + ps[3]);
+}
 
 __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                               const __grid_constant__ CUtensorMap map_k,
@@ -67,12 +101,10 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + 2 * ATC_Q_BYTES;
-    uint8_t* sP = sKV + ATC_STAGES * ATC_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * ATC_P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + ATC_SLOTS * ATC_TILE_BYTES);
     const uint32_t q_full = tc_smem(bars);
-    const uint32_t kv_full0 = q_full + 8, kv_empty0 = kv_full0 + 8 * ATC_STAGES;
-    const uint32_t s_full0 = kv_empty0 + 8 * ATC_STAGES;        // s_full[unit][buffer] at + 16 * unit + 8 * buffer
-    const uint32_t p_full0 = s_full0 + 32, o_done0 = p_full0 + 16;
+    const uint32_t full0 = q_full + 8, empty0 = full0 + 8 * ATC_SLOTS;
+    const uint32_t s_full0 = empty0 + 8 * ATC_SLOTS, p_full0 = s_full0 + 16, o_done0 = p_full0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + ATC_NUM_BARS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,9 +123,10 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < ATC_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-        for (int s = 0; s < 4; ++s) mbar_init(s_full0 + 8 * s, 1);
-        for (int u = 0; u < 2; ++u) { mbar_init(p_full0 + 8 * u, 4); mbar_init(o_done0 + 8 * u, 1); }
+        for (int s = 0; s < ATC_SLOTS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int u = 0; u < 2; ++u) {
+            mbar_init(s_full0 + 8 * u, 1); mbar_init(p_full0 + 8 * u, 4); mbar_init(o_done0 + 8 * u, 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) {
@@ -105,7 +138,6 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // S of unit u, buffer b: columns u * 128 + b * 64;  O of unit u: columns 256 + u * 128
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;
 
     pdl_wait();
@@ -117,38 +149,57 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     const int pos0 = p.row_pos[r] + q0;
     const int hi = pos0 + n_q;                                           // keys < hi are read by the tile
     int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    lo &= ~(ATC_BN - 1);                                                 // blocks start at multiples of 64 keys
+    lo &= ~(ATC_BN - 1);                                                 // blocks start at multiples of 128 keys
     const int nb = (hi - lo + ATC_BN - 1) / ATC_BN;
 
-    if (warp == 8 && lane == 0) {
+    if (warp == 8) {
         // ---------------------------------------------------------------- producer
-        mbar_expect_tx(q_full, units * ATC_Q_BYTES);
-        for (int u = 0; u < units; ++u) {
-            tma_load_2d(tc_smem(sQ) + u * ATC_Q_BYTES, &map_q, q_full, (head0 + u) * ATC_D, tok0);
-            tma_load_2d(tc_smem(sQ) + u * ATC_Q_BYTES + ATC_BM * 128, &map_q, q_full, (head0 + u) * ATC_D + 64, tok0);
+        // The whole warp: lane l looks up the cache rows of the l-th TMA box of a block (one page
+        // or 128 keys), a block ahead of the loads, so that the block-table reads of a block cost
+        // one memory latency; lane 0 issues the loads.
+        if (lane == 0) {
+            mbar_expect_tx(q_full, units * ATC_Q_BYTES);
+            for (int u = 0; u < units; ++u) {
+                tma_load_2d(tc_smem(sQ) + u * ATC_Q_BYTES, &map_q, q_full, (head0 + u) * ATC_D, tok0);
+                tma_load_2d(tc_smem(sQ) + u * ATC_Q_BYTES + ATC_BM * 128, &map_q, q_full, (head0 + u) * ATC_D + 64, tok0);
+            }
         }
         const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
         const int P = 1 << p.logP;
         const int rows_per_op = P < ATC_BN ? P : ATC_BN;               // rows one TMA box brings
+        const int n_ops = ATC_BN / rows_per_op;                          // <= 16 (pages of 8 keys or more)
         const int first_key = p.page_base[r] << p.logP;
-        for (int j = 0; j < nb; ++j) {
-            const int s = j % ATC_STAGES;
-            if (!mbar_wait(kv_empty0 + 8 * s, ((j / ATC_STAGES) & 1) ^ 1)) { atomicExch(&g_attn_tc_error, 1); break; }
-            mbar_expect_tx(kv_full0 + 8 * s, ATC_STAGE_BYTES);
-            const uint32_t base = tc_smem(sKV + s * ATC_STAGE_BYTES);
-            for (int k0 = 0; k0 < ATC_BN; k0 += rows_per_op) {
-                int key = lo + j * ATC_BN + k0;
-                // Rows no query of the tile may see (beyond the last query, or in pages a windowed
-                // request has given back) are masked later: bring any rows that exist instead.
-                if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));
-                if (key < first_key) key = first_key;
-                const int page = table[key >> p.logP];
-                const int row = ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
-                const uint32_t off = (uint32_t)k0 * 128;
-                tma_load_2d(base + off, &map_k, kv_full0 + 8 * s, 0, row);
-                tma_load_2d(base + ATC_KV_HALF + off, &map_k, kv_full0 + 8 * s, 64, row);
-                tma_load_2d(base + 2 * ATC_KV_HALF + off, &map_v, kv_full0 + 8 * s, 0, row);
-                tma_load_2d(base + 3 * ATC_KV_HALF + off, &map_v, kv_full0 + 8 * s, 64, row);
+        auto row_of = [&](int j) -> int {
+            int key = lo + j * ATC_BN + (lane < n_ops ? lane : 0) * rows_per_op;
+            // Rows no query of the tile may see (beyond the last query, or in pages a windowed
+            // request has given back) are masked later: bring any rows that exist instead.
+            if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));
+            if (key < first_key) key = first_key;
+            const int page = table[key >> p.logP];
+            return ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
+        };
+        int slot = 0, phase = 0;
+        int row_next = nb > 0 ? row_of(0) : 0;
+        bool good = true;
+        for (int j = 0; j < nb && good; ++j) {
+            const int row_cur = row_next;
+            if (j + 1 < nb) row_next = row_of(j + 1);
+            for (int kv = 0; kv < 2 && good; ++kv) {                     // the K tile of the block, then its V tile
+                bool got = mbar_wait(empty0 + 8 * slot, phase ^ 1);
+                if (!got && lane == 0) atomicExch(&g_attn_tc_error, 1);
+                good = __all_sync(0xffffffffu, got);
+                if (!good) break;
+                if (elect_one()) mbar_expect_tx(full0 + 8 * slot, ATC_TILE_BYTES);
+                const uint32_t base = tc_smem(sKV + slot * ATC_TILE_BYTES);
+                const CUtensorMap* map = kv ? &map_v : &map_k;
+                for (int l = 0; l < n_ops; ++l) {
+                    const int row = __shfl_sync(0xffffffffu, row_cur, l);
+                    if (elect_one()) {
+                        tma_load_2d(base + (uint32_t)(l * rows_per_op) * 128, map, full0 + 8 * slot, 0, row);
+                        tma_load_2d(base + ATC_HALF_BYTES + (uint32_t)(l * rows_per_op) * 128, map, full0 + 8 * slot, 64, row);
+                    }
+                }
+                if (++slot == ATC_SLOTS) { slot = 0; phase ^= 1; }
             }
         }
     } else if (warp == 9) {
@@ -164,54 +215,53 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             if (!ok && lane == 0) atomicExch(&g_attn_tc_error, code);
             return __all_sync(0xffffffffu, ok);
         };
-        bool good = wait_all(q_full, 0, 2);
-        // descriptor low words: Q per unit, first K/V stage, P per unit (see umma_bf16_lo)
+        // descriptor low words (see umma_bf16_lo): Q, and slot 0 as a K tile and as a V tile
         const uint32_t qlo = umma_lo(tc_smem(sQ)), klo0 = umma_lo(tc_smem(sKV));
-        const uint32_t vlo0 = umma_lo_mn(tc_smem(sKV) + 2 * ATC_KV_HALF, ATC_KV_HALF), plo = umma_lo(tc_smem(sP));
-        auto issue_qk = [&](int j) {
-            const int s = j & (ATC_STAGES - 1);
-            good = wait_all(kv_full0 + 8 * s, (j / ATC_STAGES) & 1, 3);
-            if (!good) return;
-            tc_fence_after();
-            const uint32_t klo = klo0 + s * (ATC_STAGE_BYTES >> 4);
-            const uint32_t sc = tmem_s + (j & 1) * ATC_BN;
+        const uint32_t vlo0 = umma_lo_mn(tc_smem(sKV), ATC_HALF_BYTES);
+        auto issue_qk = [&](int u, int slot) {                          // S_u = Q_u K^T, K in `slot`
+            const uint32_t klo = klo0 + slot * (ATC_TILE_BYTES >> 4);
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (u < units) {
-#pragma unroll
-                    for (int k = 0; k < ATC_D / 16; ++k)
-                        umma_bf16_elect(sc + u * 128, qlo + ((u * ATC_Q_BYTES + (k >> 2) * ATC_BM * 128) >> 4) + 2 * (k & 3),
-                                        klo + (((k >> 2) * ATC_KV_HALF) >> 4) + 2 * (k & 3), IDESC_QK, k > 0 ? 1u : 0u);
-                    umma_commit_elect(s_full0 + 16 * u + 8 * (j & 1));
-                }
-            }
+            for (int k = 0; k < ATC_D / 16; ++k)
+                umma_bf16_elect(tmem_s + u * 128, qlo + ((u * ATC_Q_BYTES + (k >> 2) * ATC_BM * 128) >> 4) + 2 * (k & 3),
+                                klo + (((k >> 2) * ATC_HALF_BYTES) >> 4) + 2 * (k & 3), IDESC_QK, k > 0 ? 1u : 0u);
+            umma_commit_elect(s_full0 + 8 * u);
         };
-        if (good && nb > 0) issue_qk(0);
+        bool good = wait_all(q_full, 0, 2);
+        int slot = 0, phase = 0;                                         // the next tile of the ring
+        if (good && nb > 0) {
+            good = wait_all(full0, 0, 3);
+            if (good) {
+                for (int u = 0; u < units; ++u) issue_qk(u, 0);
+                umma_commit_elect(empty0);
+                slot = 1;
+            }
+        }
         for (int j = 0; j < nb && good; ++j) {
-            // S buffer (j+1) & 1 of each unit is free: its softmax warps read block j-1 from it
-            // before they signalled p_full for j-1, which P V of block j-1 waited for.
-            if (j + 1 < nb) issue_qk(j + 1);
+            const int sv = slot, pv = phase;                             // V_j
+            if (++slot == ATC_SLOTS) { slot = 0; phase ^= 1; }
+            const int sk = slot, pk = phase;                             // K_{j+1}
+            const bool has_next = j + 1 < nb;
+            if (has_next) { if (++slot == ATC_SLOTS) { slot = 0; phase ^= 1; } }
+            good = wait_all(full0 + 8 * sv, pv, 3);
+            if (good && has_next) good = wait_all(full0 + 8 * sk, pk, 3);
             if (!good) break;
-            const int s = j & (ATC_STAGES - 1);
-            const uint32_t vlo = vlo0 + s * (ATC_STAGE_BYTES >> 4);
+            const uint32_t vlo = vlo0 + sv * (ATC_TILE_BYTES >> 4);
+            for (int u = 0; u < units && good; ++u) {
+                good = wait_all(p_full0 + 8 * u, j & 1, 4);
+                if (!good) break;
+                tc_fence_after();
+                // 16 keys a step: P advances 8 columns, V 16 rows of 128 bytes
+                umma_bf16_ts_elect(tmem_o + u * 128, tmem_s + u * 128, vlo, IDESC_PV, j > 0 ? 1u : 0u);
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (u < units && good) {
-                    good = wait_all(p_full0 + 8 * u, j & 1, 4);
-                    if (good) {
-                        tc_fence_after();
-                        // 16 keys a step: P advances 32 bytes, V 16 rows of 128 bytes
-                        umma_bf16_elect(tmem_o + u * 128, plo + ((u * ATC_P_BYTES) >> 4), vlo, IDESC_PV, j > 0 ? 1u : 0u);
-#pragma unroll
-                        for (int k = 1; k < ATC_BN / 16; ++k)
-                            umma_bf16_elect(tmem_o + u * 128, plo + ((u * ATC_P_BYTES) >> 4) + 2 * k,
-                                            vlo + ((k * 16 * 128) >> 4), IDESC_PV, 1u);
-                        umma_commit_elect(o_done0 + 8 * u);
-                    }
-                }
+                for (int k = 1; k < ATC_BN / 16; ++k)
+                    umma_bf16_ts_elect(tmem_o + u * 128, tmem_s + u * 128 + 8 * k, vlo + ((k * 16 * 128) >> 4), IDESC_PV, 1u);
+                // the next scores go where P was: the pipe runs them after the product above
+                if (has_next) issue_qk(u, sk);
+                else umma_commit_elect(o_done0 + 8 * u);
             }
             if (!good) break;
-            umma_commit_elect(kv_empty0 + 8 * s);       // both units have read the stage
+            umma_commit_elect(empty0 + 8 * sv);
+            if (has_next) umma_commit_elect(empty0 + 8 * sk);
         }
     } else if (warp < 4 * units) {
         // ---------------------------------------------------------------- softmax and output
@@ -219,36 +269,28 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         const int row = (warp & 3) * 32 + lane;                          // query row = TMEM lane
         const int head = head0 + u;
         const int qpos = pos0 + row;
+        const bool row_ok = row < n_q;
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t my_s = tmem_s + lane_addr + u * 128, my_o = tmem_o + lane_addr + u * 128;
-        const uint32_t s_full = s_full0 + 16 * u, p_full = p_full0 + 8 * u, o_done = o_done0 + 8 * u;
-        uint8_t* prow = sP + u * ATC_P_BYTES + row * 128;
+        const uint32_t s_full = s_full0 + 8 * u, p_full = p_full0 + 8 * u, o_done = o_done0 + 8 * u;
         float m_ref = -INFINITY, l_run = 0.f;
         bool good = true;
         for (int j = 0; j < nb; ++j) {
-            if (good && !mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
+            // S of block j is complete; so is P V of block j-1, issued before it: O is stable
+            if (good && !mbar_wait(s_full, j & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
             good = __all_sync(0xffffffffu, good);
             if (!good) break;
             tc_fence_after();
             const int key0 = lo + j * ATC_BN;
-            float s[ATC_BN];
-            tmem_ld64(my_s + (j & 1) * ATC_BN, s);
             // a block every query of the tile sees whole needs no mask
-            if (key0 + ATC_BN - 1 > pos0 || p.window > 0 || n_q < ATC_BM) {
-#pragma unroll
-                for (int c = 0; c < ATC_BN; ++c) {
-                    const int key = key0 + c;
-                    const bool okk = key <= qpos && row < n_q && (p.window <= 0 || key > qpos - p.window);
-                    s[c] = okk ? s[c] : -INFINITY;
-                }
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < ATC_BN; c += 4) {
-                mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
-                mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;   // the scale is positive
+            const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || n_q < ATC_BM;
+            float s[64];
+            tmem_ld64(my_s, s);
+            if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
+            float mx = atc_max(s);
+            tmem_ld64(my_s + 64, s);
+            if (masked) atc_mask(s, key0 + 64, qpos, row_ok, p.window);
+            mx = fmaxf(mx, atc_max(s)) * p.scale_log2;                   // the scale is positive
             // reference maximum: moved only when the row maximum outgrew it by more than 2^8
             float corr = 1.f;
             if (mx > m_ref + ATC_RESCALE_LOG2) {
@@ -257,56 +299,43 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                 m_ref = mx;
             }
             const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
-            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t w[ATC_BN / 2];
+            uint32_t w_lo[32], w_hi[32];
+            float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
+            tmem_ld64(my_s, s);
+            if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
+            psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
+            l_run += psum;
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-            for (int c = 0; c < ATC_BN; c += 2) {
-                const float a = fast_exp2(fmaf(s[c], p.scale_log2, neg_ref));
-                const float b = fast_exp2(fmaf(s[c + 1], p.scale_log2, neg_ref));
-                ps4[(c >> 1) & 3] += a + b;
-                __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-                w[c >> 1] = *reinterpret_cast<uint32_t*>(&v);
-            }
-            l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-            // P V of the block before has completed: the P tile is free and O is stable
-            if (j > 0) {
-                if (!mbar_wait(o_done, (j - 1) & 1)) { atomicExch(&g_attn_tc_error, 7); good = false; }
-                good = __all_sync(0xffffffffu, good);
-                if (!good) break;
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
+                for (int c = 0; c < ATC_D; c += 32) {
+                    float part[32];
+                    tmem_ld32(my_o + c, part);
 #pragma unroll
-                    for (int c = 0; c < ATC_D; c += 32) {
-                        float part[32];
-                        tmem_ld32(my_o + c, part);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) part[i] *= corr;
-                        tmem_st32(my_o + c, part);
-                    }
+                    for (int i = 0; i < 32; ++i) part[i] *= corr;
+                    tmem_st32(my_o + c, part);
                 }
             }
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)                                // 8 chunks of 8 keys (16 bytes), swizzled
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
-                    make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
-            fence_proxy_async();
+            // P over the first 64 columns of S: column c holds keys 2c and 2c + 1
+            tmem_st32_raw(my_s, w_lo);
+            tmem_st32_raw(my_s + 32, w_hi);
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
         if (good && nb > 0) {
-            if (!mbar_wait(o_done, (nb - 1) & 1)) { atomicExch(&g_attn_tc_error, 8); good = false; }
+            if (!mbar_wait(o_done, 0)) { atomicExch(&g_attn_tc_error, 8); good = false; }
             good = __all_sync(0xffffffffu, good);
         }
         if (good) {
             tc_fence_after();
-            const float inv = row < n_q ? 1.f / l_run : 0.f;
+            const float inv = row_ok ? 1.f / l_run : 0.f;
             bf16* orow = p.out + ((int64_t)(tok0 + row) * p.nq + head) * ATC_D;
 #pragma unroll
             for (int c = 0; c < ATC_D; c += 32) {
                 float part[32];
                 tmem_ld32(my_o + c, part);
-                if (row < n_q) {
+                if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint32_t ww[4];
