@@ -284,26 +284,36 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             const int key0 = lo + j * ATC_BN;
             // a block every query of the tile sees whole needs no mask
             const bool masked = key0 + ATC_BN - 1 > pos0 || p.window > 0 || n_q < ATC_BM;
+            // One pass in the common case: exponentiate against the reference maximum the row
+            // already has while the block's own maximum is taken; only a row whose maximum
+            // outgrew the reference by more than 2^8 (always so in its first block) moves the
+            // reference, and then the warp reads the block again.
             float s[64];
+            uint32_t w_lo[32], w_hi[32];
+            float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
             tmem_ld64(my_s, s);
             if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
             float mx = atc_max(s);
+            float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             tmem_ld64(my_s + 64, s);
             if (masked) atc_mask(s, key0 + 64, qpos, row_ok, p.window);
             mx = fmaxf(mx, atc_max(s)) * p.scale_log2;                   // the scale is positive
-            // reference maximum: moved only when the row maximum outgrew it by more than 2^8
             float corr = 1.f;
-            if (mx > m_ref + ATC_RESCALE_LOG2) {
-                corr = fast_exp2(m_ref - mx);                            // m_ref = -inf: 0
-                l_run *= corr;
-                m_ref = mx;
+            const bool grew = mx > m_ref + ATC_RESCALE_LOG2;
+            if (__any_sync(0xffffffffu, grew)) {
+                if (grew) {
+                    corr = fast_exp2(m_ref - mx);                        // m_ref = -inf: 0
+                    l_run *= corr;
+                    m_ref = mx;
+                    neg_ref = -m_ref;
+                }
+                psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
+                tmem_ld64(my_s, s);
+                if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
+                psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
+            } else {
+                psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
             }
-            const float neg_ref = m_ref == -INFINITY ? 0.f : -m_ref;
-            uint32_t w_lo[32], w_hi[32];
-            float psum = atc_exp_pack(s, p.scale_log2, neg_ref, w_hi);
-            tmem_ld64(my_s, s);
-            if (masked) atc_mask(s, key0, qpos, row_ok, p.window);
-            psum += atc_exp_pack(s, p.scale_log2, neg_ref, w_lo);
             l_run += psum;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
