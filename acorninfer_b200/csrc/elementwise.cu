@@ -157,17 +157,14 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 // bfloat16 rows whose block width b is a multiple of 8: 16-byte loads and stores (b8 = b / 8).
-__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int I8,
-                                     int b8) {
+// blockIdx.y is the token, so that no index is divided by the row width; a thread takes two
+// 16-byte chunks of outputs a step (four loads in flight).
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I8, int b8) {
     pdl_wait();
     pdl_trigger();
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
-         idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = idx / I8;
-        const int i = (int)(idx - t * I8);
-        const int64_t gi = t * 2 * I8 + (int64_t)(i / b8) * 2 * b8 + i % b8;
-        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + gi * 8);
-        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (gi + b8) * 8);
+    const bf16* row = gu + (int64_t)blockIdx.y * I8 * 16;
+    bf16* orow = out + (int64_t)blockIdx.y * I8 * 8;
+    auto one = [&](const uint4& g4, const uint4& u4) -> uint4 {
         const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
         uint32_t ow[4];
 #pragma unroll
@@ -177,7 +174,21 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
             __nv_bfloat162 o = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
             ow[k] = *reinterpret_cast<uint32_t*>(&o);
         }
-        *reinterpret_cast<uint4*>(out + idx * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    };
+    const int stride = gridDim.x * blockDim.x;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I8; i += 2 * stride) {
+        const int i2 = i + stride;
+        const int gi = (i / b8) * 2 * b8 + i % b8;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(row + (int64_t)gi * 8);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(row + (int64_t)(gi + b8) * 8);
+        if (i2 < I8) {
+            const int gj = (i2 / b8) * 2 * b8 + i2 % b8;
+            const uint4 g5 = *reinterpret_cast<const uint4*>(row + (int64_t)gj * 8);
+            const uint4 u5 = *reinterpret_cast<const uint4*>(row + (int64_t)(gj + b8) * 8);
+            *reinterpret_cast<uint4*>(orow + (int64_t)i2 * 8) = one(g5, u5);
+        }
+        *reinterpret_cast<uint4*>(orow + (int64_t)i * 8) = one(g4, u4);
     }
 }
 
@@ -186,12 +197,12 @@ extern "C" int acorn_swiglu(const void* gu, void* out, int tokens, int I, int bl
     const int64_t total = (int64_t)tokens * I;
     if (total <= 0) return 0;
     if (block <= 0 || I % block != 0) return ACORN_ERR_UNSUPPORTED;
-    if (dtype == ACORN_DTYPE_BF16 && block % 8 == 0) {
-        const int64_t total8 = total / 8;
-        int64_t blocks = (total8 + 255) / 256;
-        if (blocks > 148 * 16) blocks = 148 * 16;
-        return acorn_launch(swiglu_bf16x8_kernel, dim3((int)blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
-                            total8, I / 8, block / 8);
+    if (dtype == ACORN_DTYPE_BF16 && block % 8 == 0 && tokens <= 65535) {
+        const int I8 = I / 8;
+        int bx = (I8 + 511) / 512;                  // 256 threads, two chunks each
+        if (bx < 1) bx = 1;
+        return acorn_launch(swiglu_bf16x8_kernel, dim3(bx, tokens), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out,
+                            I8, block / 8);
     }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;

@@ -76,8 +76,12 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
 }
 
 // The same for the common case (whole head rotated, half pairing, head size 16, 32, 64, 128 or
-// 256): a group of d / 8 lanes per (token, head), each lane holding four rotary pairs
-// (x[4l .. 4l+3], x[d/2 + 4l .. d/2 + 4l+3]) in registers; vector loads and stores, no shared memory.
+// 256): a group of d / 8 lanes takes ROPE_HPG consecutive heads of one token, each lane holding
+// four rotary pairs (x[4l .. 4l+3], x[d/2 + 4l .. d/2 + 4l+3]) of every head in registers; vector
+// loads (all heads first, then the arithmetic) and stores, no shared memory.  The angles depend
+// on the token and the lane only, so cos and sin are computed once for the heads of a group.
+#define ROPE_HPG 4
+
 template <typename T, int G>
 __global__ void qk_rope_kv_vec_kernel(T* __restrict__ qkv, const float* __restrict__ q_w,
                                       const float* __restrict__ k_w, const float* __restrict__ inv_freq,
@@ -89,49 +93,69 @@ __global__ void qk_rope_kv_vec_kernel(T* __restrict__ qkv, const float* __restri
     pdl_wait();
     pdl_trigger();
     const int heads = write_kv ? (nq + 2 * nkv) : nq;
+    const int groups = (heads + ROPE_HPG - 1) / ROPE_HPG;                // head groups per token
     const int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
     const int l = threadIdx.x % G;
-    const bool active = item < (int64_t)tokens * heads;
+    const bool active = item < (int64_t)tokens * groups;
     const int64_t it = active ? item : 0;
-    const int t = (int)(it / heads);
-    const int h = (int)(it - (int64_t)t * heads);
-    T* src = qkv + ((int64_t)t * (nq + 2 * nkv) + h) * D;
+    const int t = (int)(it / groups);
+    const int h0 = (int)(it - (int64_t)t * groups) * ROPE_HPG;
+    T* tok = qkv + (int64_t)t * (nq + 2 * nkv) * D;
     const int pos = positions[t];
-    T* dst = src;
-    if (h >= nq) {
-        const int r = token_row[t];
-        const int kvh = (h - nq) % nkv;
-        const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
-        T* base = (h < nq + nkv) ? k_pages : v_pages;
-        dst = base + (((int64_t)page * nkv + kvh) * P + (pos % P)) * D;
-    }
-    float4 a = Vec4<T>::load(src + 4 * l), b = Vec4<T>::load(src + HALF + 4 * l);
-    if (h < nq + nkv) {
-        const float* w = (h < nq) ? q_w : k_w;
-        if (w) {
-            float ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+    float4 a[ROPE_HPG], b[ROPE_HPG];
 #pragma unroll
-            for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float inv = rsqrtf(ss / (float)D + eps);
-            const float4 wa = *reinterpret_cast<const float4*>(w + 4 * l);
-            const float4 wb = *reinterpret_cast<const float4*>(w + HALF + 4 * l);
-            a = make_float4(a.x * inv * wa.x, a.y * inv * wa.y, a.z * inv * wa.z, a.w * inv * wa.w);
-            b = make_float4(b.x * inv * wb.x, b.y * inv * wb.y, b.z * inv * wb.z, b.w * inv * wb.w);
-        }
+    for (int i = 0; i < ROPE_HPG; ++i) {
+        const int h = min(h0 + i, heads - 1);
+        a[i] = Vec4<T>::load(tok + (int64_t)h * D + 4 * l);
+        b[i] = Vec4<T>::load(tok + (int64_t)h * D + HALF + 4 * l);
+    }
+    int64_t page_off = 0;                                                // of this token's slot, in rows of D
+    if (h0 + ROPE_HPG > nq && write_kv) {
+        const int r = token_row[t];
+        const int page = block_table[(int64_t)r * table_stride + (pos / P - page_base[r])];
+        page_off = (int64_t)page * nkv * P + (pos % P);
+    }
+    float s0 = 0.f, c0 = 1.f, s1 = 0.f, c1 = 1.f, s2 = 0.f, c2 = 1.f, s3 = 0.f, c3 = 1.f;
+    if (h0 < nq + nkv) {
         const float4 f = *reinterpret_cast<const float4*>(inv_freq + 4 * l);
-        float s0, c0, s1, c1, s2, c2, s3, c3;
         sincosf((float)pos * f.x, &s0, &c0);
         sincosf((float)pos * f.y, &s1, &c1);
         sincosf((float)pos * f.z, &s2, &c2);
         sincosf((float)pos * f.w, &s3, &c3);
-        const float4 ra = make_float4(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1, a.z * c2 - b.z * s2, a.w * c3 - b.w * s3);
-        const float4 rb = make_float4(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1, b.z * c2 + a.z * s2, b.w * c3 + a.w * s3);
-        a = ra;
-        b = rb;
     }
-    if (active) {
-        Vec4<T>::store(dst + 4 * l, a);
-        Vec4<T>::store(dst + HALF + 4 * l, b);
+#pragma unroll
+    for (int i = 0; i < ROPE_HPG; ++i) {
+        const bool valid = active && h0 + i < heads;
+        const int h = min(h0 + i, heads - 1);
+        float4 x = a[i], y = b[i];
+        T* dst = tok + (int64_t)h * D;                                   // q: in place
+        if (h >= nq) {
+            const int kvh = (h - nq) % nkv;
+            dst = ((h < nq + nkv) ? k_pages : v_pages) + (page_off + (int64_t)kvh * P) * D;
+        }
+        // the sum of squares is reduced by every lane of the warp, whatever its head is: lanes of
+        // one warp hold heads of different kinds
+        float ss = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w + y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (h < nq + nkv) {
+            const float* w = (h < nq) ? q_w : k_w;
+            if (w) {
+                const float inv = rsqrtf(ss / (float)D + eps);
+                const float4 wa = *reinterpret_cast<const float4*>(w + 4 * l);
+                const float4 wb = *reinterpret_cast<const float4*>(w + HALF + 4 * l);
+                x = make_float4(x.x * inv * wa.x, x.y * inv * wa.y, x.z * inv * wa.z, x.w * inv * wa.w);
+                y = make_float4(y.x * inv * wb.x, y.y * inv * wb.y, y.z * inv * wb.z, y.w * inv * wb.w);
+            }
+            const float4 ra = make_float4(x.x * c0 - y.x * s0, x.y * c1 - y.y * s1, x.z * c2 - y.z * s2, x.w * c3 - y.w * s3);
+            const float4 rb = make_float4(y.x * c0 + x.x * s0, y.y * c1 + x.y * s1, y.z * c2 + x.z * s2, y.w * c3 + x.w * s3);
+            x = ra;
+            y = rb;
+        }
+        if (valid) {
+            Vec4<T>::store(dst + 4 * l, x);
+            Vec4<T>::store(dst + HALF + 4 * l, y);
+        }
     }
 }
 
@@ -141,7 +165,7 @@ static int launch_rope_vec(T* qkv, const float* q_w, const float* k_w, const flo
                            T* k_pages, T* v_pages, int tokens, int nq, int nkv, int P, float eps, int write_kv,
                            cudaStream_t stream) {
     const int heads = write_kv ? (nq + 2 * nkv) : nq;
-    const int64_t threads = (int64_t)tokens * heads * G;
+    const int64_t threads = (int64_t)tokens * ((heads + ROPE_HPG - 1) / ROPE_HPG) * G;
     const int64_t blocks = (threads + 255) / 256;
     return acorn_launch(qk_rope_kv_vec_kernel<T, G>, dim3((unsigned)blocks), dim3(256), 0, stream, qkv, q_w, k_w,
                         inv_freq, positions, token_row, block_table, page_base, table_stride, k_pages, v_pages, tokens,

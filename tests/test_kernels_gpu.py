@@ -63,6 +63,13 @@ def test_swiglu_and_cast(dtype):
     out = ops().swiglu(gu)
     g, u = gu.double()[:, :200], gu.double()[:, 200:]
     assert torch.allclose(out.double(), g * torch.sigmoid(g) * u, **tol(dtype))
+    # gate and up in interleaved blocks of 64 outputs, rows wider than one pass of a thread block
+    T, I, b = 5, 9 * 1024 + 64, 64
+    gu = torch.randn(T, 2 * I, device=DEV).to(dtype)
+    out = ops().swiglu(gu, block=b)
+    blocks = gu.double().view(T, I // b, 2, b)
+    g, u = blocks[:, :, 0].reshape(T, I), blocks[:, :, 1].reshape(T, I)
+    assert torch.allclose(out.double(), g * torch.sigmoid(g) * u, **tol(dtype))
     x = torch.randn(1000, device=DEV)
     assert torch.equal(ops().cast(x, torch.bfloat16), x.to(torch.bfloat16))
     assert torch.equal(ops().cast(x.to(torch.bfloat16), torch.float32), x.to(torch.bfloat16).float())
