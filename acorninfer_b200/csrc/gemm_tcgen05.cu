@@ -95,26 +95,33 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
-    if (warp == 0 && lane == 0) {
-        // ---- producer: TMA loads into the ring.  The weight tiles of the first stages do not
-        // depend on the kernel before this one, so they are requested before pdl_wait(): the
-        // weights stream while the previous kernel drains.  The token tiles (and every later
-        // stage) come after the wait.
+    if (warp == 0) {
+        // ---- producer: TMA loads into the ring (the warp stays converged, an elected lane issues).
+        // The weight tiles of the first stages do not depend on the kernel before this one, so
+        // they are requested before pdl_wait(): the weights stream while the previous kernel
+        // drains.  The token tiles (and every later stage) come after the wait.
         const int pre = nkb < STAGES ? nkb : STAGES;
         for (int i = 0; i < pre; ++i) {
-            mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-            tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
+            if (elect_one()) {
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
+            }
         }
         pdl_wait();
         for (int i = 0; i < pre; ++i)
-            tma_load_2d(tc_smem(smem + i * STAGE_BYTES) + A_BYTES, &map_x, full0 + 8 * i, (kb0 + i) * TC_BK, m0);
+            if (elect_one())
+                tma_load_2d(tc_smem(smem + i * STAGE_BYTES) + A_BYTES, &map_x, full0 + 8 * i, (kb0 + i) * TC_BK, m0);
         for (int i = pre; i < nkb; ++i) {
             const int s = i % STAGES;
-            if (!mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1)) { atomicExch(&g_gemm_tc_error, 1); break; }
-            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            const uint32_t a = tc_smem(smem + s * STAGE_BYTES);
-            tma_load_2d(a, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
-            tma_load_2d(a + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, m0);
+            bool got = mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1);
+            if (!got && lane == 0) atomicExch(&g_gemm_tc_error, 1);
+            if (!__all_sync(0xffffffffu, got)) break;
+            if (elect_one()) {
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const uint32_t a = tc_smem(smem + s * STAGE_BYTES);
+                tma_load_2d(a, &map_w, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
+                tma_load_2d(a + A_BYTES, &map_x, full0 + 8 * s, (kb0 + i) * TC_BK, m0);
+            }
         }
     } else if (warp == 1) {
         // ---- MMA issuer: the whole warp runs the loop (uniform counters and descriptors), one

@@ -80,9 +80,8 @@ __global__ void qk_rope_kv_kernel(T* __restrict__ qkv, const float* __restrict__
 // four rotary pairs (x[4l .. 4l+3], x[d/2 + 4l .. d/2 + 4l+3]) of every head in registers; vector
 // loads (all heads first, then the arithmetic) and stores, no shared memory.  The angles depend
 // on the token and the lane only, so cos and sin are computed once for the heads of a group.
-#define ROPE_HPG 4
-
-template <typename T, int G>
+// ROPE_HPG = 4 for many tokens (fewer sincos), 1 for few (a decode step: more threads, shorter chains).
+template <typename T, int G, int ROPE_HPG>
 __global__ void qk_rope_kv_vec_kernel(T* __restrict__ qkv, const float* __restrict__ q_w,
                                       const float* __restrict__ k_w, const float* __restrict__ inv_freq,
                                       const int* __restrict__ positions, const int* __restrict__ token_row,
@@ -159,17 +158,29 @@ __global__ void qk_rope_kv_vec_kernel(T* __restrict__ qkv, const float* __restri
     }
 }
 
-template <typename T, int G>
-static int launch_rope_vec(T* qkv, const float* q_w, const float* k_w, const float* inv_freq, const int* positions,
+template <typename T, int G, int ROPE_HPG>
+static int launch_rope_vec_hpg(T* qkv, const float* q_w, const float* k_w, const float* inv_freq, const int* positions,
                            const int* token_row, const int* block_table, const int* page_base, int table_stride,
                            T* k_pages, T* v_pages, int tokens, int nq, int nkv, int P, float eps, int write_kv,
                            cudaStream_t stream) {
     const int heads = write_kv ? (nq + 2 * nkv) : nq;
     const int64_t threads = (int64_t)tokens * ((heads + ROPE_HPG - 1) / ROPE_HPG) * G;
     const int64_t blocks = (threads + 255) / 256;
-    return acorn_launch(qk_rope_kv_vec_kernel<T, G>, dim3((unsigned)blocks), dim3(256), 0, stream, qkv, q_w, k_w,
-                        inv_freq, positions, token_row, block_table, page_base, table_stride, k_pages, v_pages, tokens,
-                        nq, nkv, P, eps, write_kv);
+    return acorn_launch(qk_rope_kv_vec_kernel<T, G, ROPE_HPG>, dim3((unsigned)blocks), dim3(256), 0, stream, qkv, q_w,
+                        k_w, inv_freq, positions, token_row, block_table, page_base, table_stride, k_pages, v_pages,
+                        tokens, nq, nkv, P, eps, write_kv);
+}
+
+template <typename T, int G>
+static int launch_rope_vec(T* qkv, const float* q_w, const float* k_w, const float* inv_freq, const int* positions,
+                           const int* token_row, const int* block_table, const int* page_base, int table_stride,
+                           T* k_pages, T* v_pages, int tokens, int nq, int nkv, int P, float eps, int write_kv,
+                           cudaStream_t stream) {
+    if (tokens > 256)
+        return launch_rope_vec_hpg<T, G, 4>(qkv, q_w, k_w, inv_freq, positions, token_row, block_table, page_base,
+                                            table_stride, k_pages, v_pages, tokens, nq, nkv, P, eps, write_kv, stream);
+    return launch_rope_vec_hpg<T, G, 1>(qkv, q_w, k_w, inv_freq, positions, token_row, block_table, page_base,
+                                        table_stride, k_pages, v_pages, tokens, nq, nkv, P, eps, write_kv, stream);
 }
 
 extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, const float* inv_freq,

@@ -37,9 +37,11 @@ def rope_reference(x, positions, rot, theta, interleaved):
     (4, 2, 16, 16, False, True, 4), (10, 2, 48, 48, False, True, 16), (3, 3, 80, 32, True, True, 8),
     (6, 1, 112, 112, False, False, 32), (2, 1, 272, 64, False, True, 16), (32, 8, 128, 128, False, True, 16),
     (5, 5, 64, 64, False, False, 8), (8, 1, 32, 32, False, True, 4), (2, 2, 256, 256, False, True, 16)])
-def test_qk_rope_kv(dtype, nq, nkv, d, rot, inter, norm, P):
+@pytest.mark.parametrize("qlens", [[21, 1, 2, 17], [290, 1, 2, 17]])      # few tokens / many: two shapes of the kernel
+def test_qk_rope_kv(dtype, nq, nkv, d, rot, inter, norm, P, qlens):
     theta, eps, NP = 5e5, 2e-6, 1400
-    lay = rows_layout([0, 37, 4095, 15], [21, 1, 2, 17], P, NP, seed=1)
+    befores = [0, 37, 4095, 15]
+    lay = rows_layout(befores, qlens, P, NP, seed=1)
     T = lay["num_tokens"]
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dtype)
     qw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
@@ -60,7 +62,7 @@ def test_qk_rope_kv(dtype, nq, nkv, d, rot, inter, norm, P):
     got_q = qkv.double().cpu().view(T, nq + 2 * nkv, d)[:, :nq]
     assert torch.allclose(got_q, q, **tol)
     at = 0
-    for r, (before, n) in enumerate(zip([0, 37, 4095, 15], [21, 1, 2, 17])):
+    for r, (before, n) in enumerate(zip(befores, qlens)):
         for i in range(n):
             p = before + i
             page, slot = lay["tables"][r][p // P], p % P
@@ -68,7 +70,7 @@ def test_qk_rope_kv(dtype, nq, nkv, d, rot, inter, norm, P):
             assert torch.equal(v_pages[page, :, slot].cpu(), qkv.cpu().view(T, -1, d)[at + i, nq + nkv:])
         at += n
     # pages of other rows and untouched slots stay zero
-    used = {(lay["tables"][r][(b + i) // P], (b + i) % P) for r, (b, n) in enumerate(zip([0, 37, 4095, 15], [21, 1, 2, 17])) for i in range(n)}
+    used = {(lay["tables"][r][(b + i) // P], (b + i) % P) for r, (b, n) in enumerate(zip(befores, qlens)) for i in range(n)}
     mask = torch.ones(NP, P, dtype=torch.bool)
     for pg, sl in used:
         mask[pg, sl] = False
