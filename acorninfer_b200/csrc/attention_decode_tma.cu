@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + DT_STAGES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (tc_smem(smem) & 1023u) {
-        if (threadIdx.x == 0) atomicExch(&g_attn_dec_tma_error, 9);
+        if (threadIdx.x == 0) tc_fail(&g_attn_dec_tma_error, 9, ACORN_KERNEL_ATTN_DECODE_TMA);
         return;
     }
     if (threadIdx.x == 0) {
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
             const int first_key = p.page_base[r] << p.logP;
             for (int c = c0; c < c1; ++c) {
                 const int i = c - c0, s = i % DT_STAGES;
-                if (!mbar_wait(empty0 + 8 * s, ((i / DT_STAGES) & 1) ^ 1)) { atomicExch(&g_attn_dec_tma_error, 1); break; }
+                if (!mbar_wait(empty0 + 8 * s, ((i / DT_STAGES) & 1) ^ 1)) { tc_fail(&g_attn_dec_tma_error, 1, ACORN_KERNEL_ATTN_DECODE_TMA); break; }
                 mbar_expect_tx(full0 + 8 * s, DT_STAGE_BYTES);
                 const uint32_t base = tc_smem(smem + s * DT_STAGE_BYTES);
                 for (int k0 = 0; k0 < DT_CHUNK; k0 += rows_per_op) {
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
         bool good = true;
         for (int c = c0; c < c1; ++c) {
             const int i = c - c0, s = i % DT_STAGES;
-            if (good && !mbar_wait(full0 + 8 * s, (i / DT_STAGES) & 1)) { atomicExch(&g_attn_dec_tma_error, 2); good = false; }
+            if (good && !mbar_wait(full0 + 8 * s, (i / DT_STAGES) & 1)) { tc_fail(&g_attn_dec_tma_error, 2, ACORN_KERNEL_ATTN_DECODE_TMA); good = false; }
             good = __all_sync(0xffffffffu, good);
             if (!good) break;
             const int wkey0 = base_key + c * DT_CHUNK + warp * 16;      // first key of this warp's 16
@@ -274,3 +274,5 @@ extern "C" int acorn_attention_decode_tma_error() {
     if (v != 0) cudaMemcpyToSymbol(g_attn_dec_tma_error, &zero, sizeof(int));
     return v;
 }
+
+ACORN_ERROR_WORD_SETTER(acorn_attention_decode_tma_set_error_word)

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     const int head0 = kvh * rep + 2 * pair;
     const int units = (2 * pair + 1 < rep) ? 2 : 1;
     if (tc_smem(smem) & 1023u) {            // the swizzled tiles need a 1024-byte aligned base
-        if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 9);
+        if (threadIdx.x == 0) tc_fail(&g_attn_tc_error, 9, ACORN_KERNEL_ATTN_PREFILL_TC);
         return;
     }
 
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             if (j + 1 < nb) row_next = row_of(j + 1);
             for (int kv = 0; kv < 2 && good; ++kv) {                     // the K tile of the block, then its V tile
                 bool got = mbar_wait(empty0 + 8 * slot, phase ^ 1);
-                if (!got && lane == 0) atomicExch(&g_attn_tc_error, 1);
+                if (!got && lane == 0) tc_fail(&g_attn_tc_error, 1, ACORN_KERNEL_ATTN_PREFILL_TC);
                 good = __all_sync(0xffffffffu, got);
                 if (!good) break;
                 if (elect_one()) mbar_expect_tx(full0 + 8 * slot, ATC_TILE_BYTES);
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
                                       ((uint32_t)(ATC_D >> 3) << 17) | ((uint32_t)(ATC_BM >> 4) << 24);
         auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
             bool ok = mbar_wait(bar, parity);
-            if (!ok && lane == 0) atomicExch(&g_attn_tc_error, code);
+            if (!ok && lane == 0) tc_fail(&g_attn_tc_error, code, ACORN_KERNEL_ATTN_PREFILL_TC);
             return __all_sync(0xffffffffu, ok);
         };
         // descriptor low words (see umma_bf16_lo): Q, and slot 0 as a K tile and as a V tile
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
         bool good = true;
         for (int j = 0; j < nb; ++j) {
             // S of block j is complete; so is P V of block j-1, issued before it: O is stable
-            if (good && !mbar_wait(s_full, j & 1)) { atomicExch(&g_attn_tc_error, 6); good = false; }
+            if (good && !mbar_wait(s_full, j & 1)) { tc_fail(&g_attn_tc_error, 6, ACORN_KERNEL_ATTN_PREFILL_TC); good = false; }
             good = __all_sync(0xffffffffu, good);
             if (!good) break;
             tc_fence_after();
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
             if (lane == 0) mbar_arrive(p_full);
         }
         if (good && nb > 0) {
-            if (!mbar_wait(o_done, 0)) { atomicExch(&g_attn_tc_error, 8); good = false; }
+            if (!mbar_wait(o_done, 0)) { tc_fail(&g_attn_tc_error, 8, ACORN_KERNEL_ATTN_PREFILL_TC); good = false; }
             good = __all_sync(0xffffffffu, good);
         }
         if (good) {
@@ -414,3 +414,5 @@ extern "C" int acorn_attention_tc_error() {
     if (v != 0) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
     return v;
 }
+
+ACORN_ERROR_WORD_SETTER(acorn_attention_tc_set_error_word)

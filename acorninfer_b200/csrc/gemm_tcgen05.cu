@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         for (int i = pre; i < nkb; ++i) {
             const int s = i % STAGES;
             bool got = mbar_wait(empty0 + 8 * s, ((i / STAGES) & 1) ^ 1);
-            if (!got && lane == 0) atomicExch(&g_gemm_tc_error, 1);
+            if (!got && lane == 0) tc_fail(&g_gemm_tc_error, 1, ACORN_KERNEL_GEMM_TC);
             if (!__all_sync(0xffffffffu, got)) break;
             if (elect_one()) {
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         for (int i = 0; i < nkb; ++i) {
             const int s = i % STAGES;
             bool got = mbar_wait(full0 + 8 * s, (i / STAGES) & 1);
-            if (!got && lane == 0) atomicExch(&g_gemm_tc_error, 2);
+            if (!got && lane == 0) tc_fail(&g_gemm_tc_error, 2, ACORN_KERNEL_GEMM_TC);
             if (!__all_sync(0xffffffffu, got)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t alo = alo0 + s * (STAGE_BYTES >> 4), blo = blo0 + s * (STAGE_BYTES >> 4);
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     pdl_wait();          // the output buffer may still be read by the kernel before this one
     pdl_trigger();
     if (nkb > 0) ok = mbar_wait(accum_bar, 0);
-    if (!ok) atomicExch(&g_gemm_tc_error, 3);
+    if (!ok) tc_fail(&g_gemm_tc_error, 3, ACORN_KERNEL_GEMM_TC);
     ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below is warp-wide
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int n = n0 + warp * 32 + lane;
@@ -357,3 +357,5 @@ extern "C" int acorn_gemm_tc_error() {
     if (v != 0) cudaMemcpyToSymbol(g_gemm_tc_error, &zero, sizeof(int));
     return v;
 }
+
+ACORN_ERROR_WORD_SETTER(acorn_gemm_tc_set_error_word)

@@ -8,6 +8,31 @@
 
 #define TC_WAIT_LIMIT (1u << 22)
 
+// A kernel whose bounded wait gives up records where in its own flag and in a word of pinned,
+// device-mapped host memory, which the host reads without a CUDA call (so it can look after
+// every step).  The pointer is set once per library load, per translation unit
+// (ACORN_ERROR_WORD_SETTER); the word holds kernel * 100 + point.
+#define ACORN_KERNEL_GEMM_TC 1
+#define ACORN_KERNEL_ATTN_PREFILL_TC 2
+#define ACORN_KERNEL_ATTN_DECODE_TMA 3
+#define ACORN_KERNEL_SELFTEST 9
+
+static __device__ int* g_error_word = nullptr;
+
+__device__ __forceinline__ void tc_fail(int* flag, int point, int kernel) {
+    atomicExch(flag, point);
+    int* w = g_error_word;
+    if (w != nullptr) {
+        *reinterpret_cast<volatile int*>(w) = kernel * 100 + point;
+        __threadfence_system();
+    }
+}
+
+#define ACORN_ERROR_WORD_SETTER(fn)                                                              \
+    extern "C" int fn(int* device_ptr) {                                                          \
+        return (int)cudaMemcpyToSymbol(g_error_word, &device_ptr, sizeof(device_ptr));            \
+    }
+
 __device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -40,7 +40,44 @@ def lib():
                 fn.argtypes = getattr(_Sigs, name)
                 fn.restype = c_int
         _lib.acorn_uniform.restype = c_float
+        _init_error_word(_lib)
     return _lib
+
+
+_error_word: ctypes.c_int | None = None       # pinned host memory that kernels write when a bounded wait gives up
+_KERNEL_NAMES = {1: "gemm_tcgen05", 2: "attention_prefill_tc", 3: "attention_decode_tma", 9: "error-word self-test"}
+
+
+def _init_error_word(library) -> None:
+    global _error_word
+    host, dev = c_void_p(), c_void_p()
+    code = library.acorn_error_word_alloc(ctypes.byref(host), ctypes.byref(dev))
+    if code != 0 or not host.value:
+        raise KernelError(f"could not allocate the kernels' error word: CUDA error {code}")
+    for setter in ("acorn_gemm_tc_set_error_word", "acorn_attention_tc_set_error_word",
+                   "acorn_attention_decode_tma_set_error_word", "acorn_selftest_set_error_word"):
+        code = getattr(library, setter)(dev)
+        if code != 0:
+            raise KernelError(f"{setter}: CUDA error {code}")
+    _error_word = ctypes.c_int.from_address(host.value)
+
+
+def raise_on_kernel_error() -> None:
+    """Raises if a kernel of a step that has completed gave up a bounded wait (its results are not
+    valid).  Costs a read of host memory: callers look after every step whose results they read."""
+    if _error_word is None or _error_word.value == 0:
+        return
+    word = _error_word.value
+    _error_word.value = 0
+    for getter in (gemm_tc_error, attention_tc_error, attention_decode_tma_error):      # clear the kernels' own flags
+        getter()
+    raise KernelError(f"kernel {_KERNEL_NAMES.get(word // 100, word // 100)} gave up a bounded wait at point "
+                      f"{word % 100}: the results of the step are not valid")
+
+
+def error_word_selftest(point: int) -> None:
+    """Launches a kernel that does nothing but report ``point`` the way a failing kernel would."""
+    _ok(lib().acorn_error_word_selftest(point, _stream()), "error_word_selftest")
 
 
 class _Sigs:
@@ -84,6 +121,12 @@ class _Sigs:
     acorn_sample = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_void_p, c_void_p]
     acorn_uniform = [ctypes.c_uint64, ctypes.c_uint64]
+    acorn_error_word_alloc = [c_void_p, c_void_p]
+    acorn_error_word_selftest = [c_int, c_void_p]
+    acorn_gemm_tc_set_error_word = [c_void_p]
+    acorn_attention_tc_set_error_word = [c_void_p]
+    acorn_attention_decode_tma_set_error_word = [c_void_p]
+    acorn_selftest_set_error_word = [c_void_p]
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)

@@ -80,6 +80,7 @@ class TraceSession:
         import torch
 
         from .engine.batch import StepEntry
+        from .kernels import ops
 
         entries = []
         for e in msg.get("entries", []):
@@ -93,6 +94,7 @@ class TraceSession:
             logits = self.runner.step(entries)
             if logits is not None:
                 out = logits.detach().to("cpu", torch.float32).contiguous().numpy()
+                ops.raise_on_kernel_error()     # the copy waited for the step: a kernel that gave up has said so
         for rid in msg.get("end", []):
             rc = self.live.pop(str(rid), None)
             if rc is not None:

@@ -26,6 +26,7 @@ class Sampled:
 
     def read(self) -> list[int]:
         self.event.synchronize()
+        ops.raise_on_kernel_error()
         toks = self.host.tolist()
         if any(t < 0 for t in toks):
             raise ValueError("logits contain NaN or infinity: the model's forward pass is broken")
@@ -75,6 +76,7 @@ class Sampler:
     def read(tokens: torch.Tensor) -> list[int]:
         """Brings sampled ids to the host (waits for the step that sampled them)."""
         toks = tokens.tolist()
+        ops.raise_on_kernel_error()
         if any(t < 0 for t in toks):
             raise ValueError("logits contain NaN or infinity: the model's forward pass is broken")
         return toks

@@ -67,3 +67,28 @@ def test_other_head_sizes_take_the_cp_async_decode_kernel_and_captured_steps_are
     c = counts_of(lambda: [runner.step([StepEntry(a, [t], [0])]) for t in (1, 2, 3, 4, 5)])
     assert runner.graph_replays == 3                 # seen, captured, then replayed three times
     assert c.get("attention_decode", 0) >= 2 * tiny["cfg"].num_hidden_layers and "attention_decode_tma" not in c
+
+
+def test_a_kernel_that_gives_up_a_wait_becomes_an_exception_at_the_next_read(tmp_path):
+    """Kernels report a bounded wait that gave up through a word of pinned host memory.  A kernel
+    that only reports (nothing goes wrong on the device) shows the way from there to the host."""
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.kernels import ops
+    from acorninfer_b200.sampling.sampler import Sampler
+    ops.raise_on_kernel_error()                          # nothing reported so far
+    ops.error_word_selftest(7)
+    torch.cuda.synchronize()
+    with pytest.raises(ops.KernelError, match="self-test.*point 7"):
+        ops.raise_on_kernel_error()
+    ops.raise_on_kernel_error()                          # reading clears it
+    # the sampler's read is such a point
+    ops.error_word_selftest(3)
+    ids = torch.zeros(2, dtype=torch.int32, device="cuda:0")
+    with pytest.raises(ops.KernelError, match="point 3"):
+        Sampler.read(ids)
+    # and a step afterwards is clean
+    runner = runner_for(tmp_path, TINY_B, "bfloat16")
+    a = runner.open("a")
+    logits = runner.step([StepEntry(a, [1, 2, 3], [2])])
+    assert torch.isfinite(logits).all()
+    ops.raise_on_kernel_error()
