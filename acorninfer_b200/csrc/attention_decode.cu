@@ -206,16 +206,10 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const Dec
 // head dimensions over the splits.
 #define DEC_MAX_SPLITS 32
 
-// One CTA per (token, head), MERGE_GROUPS * D threads: thread (g, i) adds the splits g, g +
-// MERGE_GROUPS, ... of output element i (its loads are independent, so they are in flight
-// together), and the groups' sums are added in group order through shared memory.
-#define MERGE_GROUPS 4
-
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                               bf16* __restrict__ out, const int* __restrict__ token_list, int nq,
                                               int D, int num_splits) {
     __shared__ float wgt[DEC_MAX_SPLITS];
-    extern __shared__ float red[];                           // [MERGE_GROUPS - 1][D]
     pdl_wait();
     pdl_trigger();
     const int ti = blockIdx.x, head = blockIdx.y;
@@ -229,22 +223,14 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
         if (threadIdx.x < num_splits) wgt[threadIdx.x] = w / wsum;
     }
     __syncthreads();
-    const int g = threadIdx.x / D, i = threadIdx.x - g * D;
-    float acc = 0.f;
-#pragma unroll
-    for (int k = 0; k < DEC_MAX_SPLITS / MERGE_GROUPS; ++k) {
-        const int s = g + k * MERGE_GROUPS;
-        if (s < num_splits) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < num_splits; ++s) {
             const float w = wgt[s];
             const float v = part_o[(slot0 + s) * D + i];
             acc += w > 0.f ? w * v : 0.f;                   // an empty split left its slot unwritten
         }
-    }
-    if (g > 0) red[(g - 1) * D + i] = acc;
-    __syncthreads();
-    if (g == 0) {
-#pragma unroll
-        for (int q = 0; q < MERGE_GROUPS - 1; ++q) acc += red[q * D + i];
         out[((int64_t)t * nq + head) * D + i] = __float2bfloat16_rn(acc);
     }
 }
@@ -272,10 +258,8 @@ extern "C" int acorn_attention_decode_merge(const float* part_o, const float* pa
                                             cudaStream_t stream) {
     if (n <= 0 || num_splits <= 1) return 0;
     if (num_splits > DEC_MAX_SPLITS || n > 65535 || nq > 65535) return ACORN_ERR_UNSUPPORTED;
-    if (d > 256) return ACORN_ERR_UNSUPPORTED;
-    return acorn_launch(attention_decode_merge_kernel, dim3(n, nq), dim3(MERGE_GROUPS * d),
-                        (size_t)(MERGE_GROUPS - 1) * d * sizeof(float), stream, part_o, part_lse, (bf16*)out, token_list,
-                        nq, d, num_splits);
+    return acorn_launch(attention_decode_merge_kernel, dim3(n, nq), dim3(d >= 128 ? 128 : 64), 0, stream, part_o,
+                        part_lse, (bf16*)out, token_list, nq, d, num_splits);
 }
 
 // Sizes this kernel takes: head_dim a multiple of 16 up to 128, or 256; nq / nkv <= 16.
@@ -317,5 +301,7 @@ extern "C" int acorn_attention_decode(const void* q, int64_t q_stride, void* out
         default: return ACORN_ERR_UNSUPPORTED;
     }
     if (rc != 0 || num_splits == 1) return rc;
-    return acorn_attention_decode_merge(part_o, part_lse, out, token_list, n, nq, d, num_splits, stream);
+    dim3 grid(n, nq);
+    return acorn_launch(attention_decode_merge_kernel, grid, dim3(d >= 128 ? 128 : 64), 0, stream,
+                        (const float*)part_o, (const float*)part_lse, (bf16*)out, token_list, nq, d, num_splits);
 }
