@@ -7,11 +7,12 @@
 // 64-element step along K, TMA brings a [128 x 64] tile of W and a [MB x 64] tile of x into a
 // ring of shared-memory stages (128-byte swizzle, K-major); one elected thread issues four
 // tcgen05.mma (M=128, N=MB, K=16) per stage into a [128 lanes x MB columns] float32 accumulator
-// in tensor memory; tcgen05.commit frees the stage.  When the K range is split (SPLITS > 1) the
-// CTAs of one output tile form a thread-block cluster, each reduces its share of K, and the
-// partial tiles are summed through distributed shared memory in a fixed order (deterministic,
-// no scratch in global memory).  The epilogue reads the accumulator with tcgen05.ld, lane =
-// output column, and writes out[m, n] as bfloat16 or float32.
+// in tensor memory; tcgen05.commit frees the stage.  When the K range is split (SPLITS > 1, tiles
+// of up to 32 tokens) the CTAs of one output tile form a thread-block cluster, each reduces its
+// share of K, and the partial tiles are exchanged by rows through distributed shared memory:
+// every CTA reads its accumulator with tcgen05.ld (lane = output column) and stores each row
+// into the CTA that finishes it, which adds the partial rows in rank order (deterministic, no
+// scratch in global memory, one cluster barrier) and writes out[m, n] as bfloat16 or float32.
 //
 // The kernel is launched with programmatic stream serialization: the weight tiles of the first
 // stages are requested before griddepcontrol.wait, so the weights start to stream while the
@@ -53,6 +54,14 @@ struct TcParams {
     float* ss_out;           // [ceil(N / 128), M]
 };
 
+// A load that the compiler leaves where it is written (it may not sink it below a barrier to the
+// first use of the value).
+__device__ __forceinline__ float ld_global_now(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ------------------------------------------------------------------ the kernel
 
 template <int MB, int STAGES>
@@ -79,10 +88,26 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     const int kb0 = (int)((int64_t)p.kblocks * split / splits), kb1 = (int)((int64_t)p.kblocks * (split + 1) / splits);
     const int nkb = kb1 - kb0;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(accum_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // every CTA of the cluster says that it runs; the epilogue waits for all of them to have said
+    // so before it writes into their shared memory
+    if (splits > 1) cg::this_cluster().barrier_arrive();
+    const int pre = nkb < STAGES ? nkb : STAGES;
+    if (warp == 0) {
+        // Barriers, then at once the weight tiles of the first stages: they do not depend on the
+        // kernel before this one, so they are requested before pdl_wait() and before the rest of
+        // the CTA has set itself up; the weights stream while the previous kernel drains.
+        if (lane == 0) {
+            for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+            mbar_init(accum_bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        for (int i = 0; i < pre; ++i) {
+            if (elect_one()) {
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
+            }
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -96,17 +121,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     bool ok = true;
 
     if (warp == 0) {
-        // ---- producer: TMA loads into the ring (the warp stays converged, an elected lane issues).
-        // The weight tiles of the first stages do not depend on the kernel before this one, so
-        // they are requested before pdl_wait(): the weights stream while the previous kernel
-        // drains.  The token tiles (and every later stage) come after the wait.
-        const int pre = nkb < STAGES ? nkb : STAGES;
-        for (int i = 0; i < pre; ++i) {
-            if (elect_one()) {
-                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-                tma_load_2d(tc_smem(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
-            }
-        }
+        // ---- producer: the token tiles of the first stages and every later stage come after the
+        // wait (the warp stays converged, an elected lane issues)
         pdl_wait();
         for (int i = 0; i < pre; ++i)
             if (elect_one())
@@ -154,25 +170,43 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     const int m_valid = min(MB, p.M - m0);
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
-    // The accumulator tile goes to this CTA's shared memory as [MB][128] float32 (the ring is
-    // drained: every stage was consumed before accum_bar completed).  With a split K range the
-    // tiles of the cluster's CTAs are then summed in rank order, each CTA finishing the rows
-    // m = rank, rank + csize, ...; without a split the CTA finishes all rows of its own tile.
-    float* part = reinterpret_cast<float*>(smem);
+    // The output tile is finished by rows: row m by the CTA of rank m % csize of the cluster (all
+    // rows by the one CTA when K is not split).  Every CTA sends its partial rows from tensor
+    // memory straight into the receive buffers of their owners (remote shared-memory stores, which
+    // do not wait), the cluster meets once, and each CTA adds up, in rank order, the partial rows
+    // it received: recv[q][i][128] is row rank + i * csize as computed by rank q.  For tiles of up
+    // to 32 tokens the buffer lies outside the ring, because a peer may still be in its main loop
+    // when rows arrive; larger tiles are never split and use the drained ring.
     constexpr int RED_FLOATS = 4 * MB > TC_THREADS ? 4 * MB : TC_THREADS;
     float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // reduction scratch, then inv[MB]
     float* inv_s = red + RED_FLOATS;
+    float* recv = MB <= 32 ? inv_s + MB : reinterpret_cast<float*>(smem);
+    int rank = 0, csize = 1;
+    if (splits > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        rank = (int)cluster.block_rank();
+        csize = (int)cluster.num_blocks();
+    }
+    const int slots = (MB + csize - 1) / csize;
+    if (splits > 1) cg::this_cluster().barrier_wait();
+    {
+        const uint32_t mine = tc_smem(recv) + (uint32_t)((rank * slots * TC_BM + warp * 32 + lane) * 4);
+        int owner = 0, slot = 0;                                      // of row c + i
 #pragma unroll
-    for (int c = 0; c < MB; c += 16) {
-        float v[16];
-        if (ok && nkb > 0) {
-            tmem_ld16(taddr + c, v);
-        } else {
+        for (int c = 0; c < MB; c += 16) {
+            float v[16];
+            if (ok && nkb > 0) {
+                tmem_ld16(taddr + c, v);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if (c + i < m_valid) st_cluster_f32(cluster_map(mine + (uint32_t)(slot * TC_BM * 4), owner), v[i]);
+                if (++owner == csize) { owner = 0; ++slot; }
+            }
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) part[(c + i) * TC_BM + warp * 32 + lane] = v[i];
     }
     // Rows of x that arrive un-normalised (x = residual * norm weight): the factor
     // rsqrt(mean(residual^2) + eps) of each row is applied to the product here.
@@ -194,27 +228,37 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     } else if (threadIdx.x < MB) {
         inv_s[threadIdx.x] = 1.f;
     }
-    int rank = 0, csize = 1;
-    if (splits > 1) {
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        rank = (int)cluster.block_rank();
-        csize = (int)cluster.num_blocks();
-    } else {
-        __syncthreads();
-    }
     const int col = threadIdx.x;                                      // 128 threads = 128 columns of the tile
-    auto tile_sum = [&](int m, int c) -> float {
-        if (splits == 1) return part[m * TC_BM + c];
-        cg::cluster_group cluster = cg::this_cluster();
-        float acc = 0.f;
-        for (int q = 0; q < csize; ++q) acc += cluster.map_shared_rank(part, q)[m * TC_BM + c];
+    const bool n_ok = n0 + col < p.N;
+    // What the ADD_NORM epilogue reads from global memory is requested before the cluster meets,
+    // so that it arrives while the CTAs wait for one another.
+    constexpr int MAX_ROWS = MB <= 64 ? MB : 1;                       // the host refuses ADD_NORM for larger tiles
+    float r_old[MAX_ROWS];
+    float nw = 0.f;
+    if (p.mode == TC_MODE_ADD_NORM) {
+        if (n_ok) nw = ld_global_now(p.norm_w + n0 + col);
+#pragma unroll
+        for (int i = 0; i < MAX_ROWS; ++i) {
+            const int m = rank + i * csize;
+            r_old[i] = (m < m_valid && n_ok) ? ld_global_now(p.resid + (int64_t)(m0 + m) * p.ldr + n0 + col) : 0.f;
+        }
+    }
+    if (splits > 1) cg::this_cluster().sync();
+    else __syncthreads();
+    // row rank + i * csize, column c: the partial sums in rank order (independent loads)
+    auto tile_sum = [&](int i, int c) -> float {
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = q < csize ? recv[(q * slots + i) * TC_BM + c] : 0.f;
+        float acc = v[0];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) acc += v[q];
         return acc;
     };
     if (p.mode == TC_MODE_PLAIN) {
-        for (int m = rank; m < m_valid; m += csize) {
-            const float val = tile_sum(m, col) * inv_s[m];
-            if (n0 + col < p.N) {
+        for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
+            const float val = tile_sum(i, col) * inv_s[m];
+            if (n_ok) {
                 const int64_t o = (int64_t)(m0 + m) * p.ldo + n0 + col;
                 if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = val;
                 else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
@@ -222,9 +266,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         }
     } else if (p.mode == TC_MODE_SWIGLU) {
         // the tile holds 64 gate columns, then the 64 up columns of the same outputs
-        for (int m = rank; m < m_valid; m += csize) {
+        for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
             if (col < 64) {
-                const float g = tile_sum(m, col) * inv_s[m], u = tile_sum(m, col + 64) * inv_s[m];
+                const float g = tile_sum(i, col) * inv_s[m], u = tile_sum(i, col + 64) * inv_s[m];
                 const int oc = blockIdx.x * 64 + col;
                 if (oc < p.N / 2)
                     reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + oc] =
@@ -234,20 +278,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     } else {
         // TC_MODE_ADD_NORM: residual += product; out = bf16(residual * norm weight), not yet
         // scaled; this tile's share of sum(residual^2) per row goes to ss_out[tile][row]
-        constexpr int MAX_ROWS = MB <= 64 ? MB : 1;     // the host refuses this mode for larger tiles
         float sq[MAX_ROWS];
 #pragma unroll
         for (int i = 0; i < MAX_ROWS; ++i) {
             sq[i] = 0.f;
             const int m = rank + i * csize;
             if (m < m_valid) {
-                const float val = tile_sum(m, col) * inv_s[m];
-                if (n0 + col < p.N) {
-                    const int64_t ri = (int64_t)(m0 + m) * p.ldr + n0 + col;
-                    const float r = p.resid[ri] + val;
-                    p.resid[ri] = r;
-                    reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + n0 + col] =
-                        __float2bfloat16_rn(r * p.norm_w[n0 + col]);
+                const float val = tile_sum(i, col) * inv_s[m];
+                if (n_ok) {
+                    const float r = r_old[i] + val;
+                    p.resid[(int64_t)(m0 + m) * p.ldr + n0 + col] = r;
+                    reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + n0 + col] = __float2bfloat16_rn(r * nw);
                     sq[i] = r * r;
                 }
             }
@@ -265,7 +306,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
                                                               red[2 * MB + threadIdx.x] + red[3 * MB + threadIdx.x];
         }
     }
-    if (splits > 1) cg::this_cluster().sync();     // peers may still be reading this CTA's tile
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -282,7 +322,9 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
     const size_t ring = (size_t)STAGES * STAGE_BYTES;
     const size_t part = (size_t)MB * TC_BM * sizeof(float);
-    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 + ((4 * MB > TC_THREADS ? 4 * MB : TC_THREADS) + MB) * sizeof(float) + 1024;
+    const size_t recv = MB <= 32 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
+    const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 +
+                        ((4 * MB > TC_THREADS ? 4 * MB : TC_THREADS) + MB) * sizeof(float) + recv + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MB, STAGES>,
@@ -331,14 +373,15 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
     p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.ss_out = ss_out;
     if (splits > p.kblocks) splits = p.kblocks;
     const int mb = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    if (mb > 32) splits = 1;               // K is split only for tiles of up to 32 tokens
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, ldw, TC_BK, TC_BM);
     if (rc) return rc;
     rc = make_map(&mx, x, M, K, ldx, TC_BK, mb);
     if (rc) return rc;
     switch (mb) {
-        case 16: return launch_tc<16, 6>(mw, mx, p, splits, stream);
-        case 32: return launch_tc<32, 5>(mw, mx, p, splits, stream);
+        case 16: return launch_tc<16, 5>(mw, mx, p, splits, stream);     // two CTAs to an SM: about 105 KB each
+        case 32: return launch_tc<32, 4>(mw, mx, p, splits, stream);
         case 64: return launch_tc<64, 4>(mw, mx, p, splits, stream);
         default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
     }
