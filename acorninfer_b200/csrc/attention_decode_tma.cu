@@ -84,27 +84,44 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
 
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
-        if (lane == 0) {
-            const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
-            const int P = 1 << p.logP;
-            const int rows_per_op = P < DT_CHUNK ? P : DT_CHUNK;
-            const int first_key = p.page_base[r] << p.logP;
-            for (int c = c0; c < c1; ++c) {
-                const int i = c - c0, s = i % DT_STAGES;
-                if (!mbar_wait(empty0 + 8 * s, ((i / DT_STAGES) & 1) ^ 1)) { tc_fail(&g_attn_dec_tma_error, 1, ACORN_KERNEL_ATTN_DECODE_TMA); break; }
-                mbar_expect_tx(full0 + 8 * s, DT_STAGE_BYTES);
-                const uint32_t base = tc_smem(smem + s * DT_STAGE_BYTES);
-                for (int k0 = 0; k0 < DT_CHUNK; k0 += rows_per_op) {
-                    int key = base_key + c * DT_CHUNK + k0;
-                    if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));      // masked later: any rows that exist
-                    if (key < first_key) key = first_key;
-                    const int page = table[key >> p.logP];
-                    const int row = ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
-                    const uint32_t off = (uint32_t)k0 * 128;
-                    tma_load_2d(base + off, &map_k, full0 + 8 * s, 0, row);
-                    tma_load_2d(base + DT_HALF_BYTES + off, &map_k, full0 + 8 * s, 64, row);
-                    tma_load_2d(base + 2 * DT_HALF_BYTES + off, &map_v, full0 + 8 * s, 0, row);
-                    tma_load_2d(base + 3 * DT_HALF_BYTES + off, &map_v, full0 + 8 * s, 64, row);
+        // The whole warp: lane l looks up the cache rows of the l-th TMA box (one page or 64 keys)
+        // of a batch of 32 boxes, a batch ahead of the loads, so that the block-table reads cost
+        // one memory latency a batch; an elected lane issues the loads.
+        const int* table = p.block_table + (int64_t)r * p.table_stride - p.page_base[r];
+        const int P = 1 << p.logP;
+        const int rows_per_op = P < DT_CHUNK ? P : DT_CHUNK;
+        const int log_ops = 6 - (p.logP < 6 ? p.logP : 6);             // boxes a chunk: 64 / rows_per_op
+        const int n_ops = (c1 - c0) << log_ops;
+        const int first_key = p.page_base[r] << p.logP;
+        auto row_of = [&](int idx) -> int {                              // box idx of this CTA's chunks
+            int key = base_key + c0 * DT_CHUNK + (idx < n_ops ? idx : 0) * rows_per_op;
+            if (key >= hi) key = hi - 1 - ((hi - 1) & (rows_per_op - 1));  // masked later: any rows that exist
+            if (key < first_key) key = first_key;
+            const int page = table[key >> p.logP];
+            return ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
+        };
+        int rows_next = row_of(lane);
+        bool good = true;
+        for (int b0 = 0; b0 < n_ops && good; b0 += 32) {
+            const int rows_cur = rows_next;
+            if (b0 + 32 < n_ops) rows_next = row_of(b0 + 32 + lane);
+            const int n_here = min(32, n_ops - b0);
+            for (int l = 0; l < n_here; ++l) {
+                const int idx = b0 + l, i = idx >> log_ops, k = idx & ((1 << log_ops) - 1), s = i % DT_STAGES;
+                if (k == 0) {                                            // first box of a chunk: its stage must be free
+                    bool got = mbar_wait(empty0 + 8 * s, ((i / DT_STAGES) & 1) ^ 1);
+                    if (!got && lane == 0) tc_fail(&g_attn_dec_tma_error, 1, ACORN_KERNEL_ATTN_DECODE_TMA);
+                    good = __all_sync(0xffffffffu, got);
+                    if (!good) break;
+                    if (elect_one()) mbar_expect_tx(full0 + 8 * s, DT_STAGE_BYTES);
+                }
+                const int row = __shfl_sync(0xffffffffu, rows_cur, l);
+                if (elect_one()) {
+                    const uint32_t dst = tc_smem(smem + s * DT_STAGE_BYTES) + (uint32_t)(k * rows_per_op) * 128;
+                    tma_load_2d(dst, &map_k, full0 + 8 * s, 0, row);
+                    tma_load_2d(dst + DT_HALF_BYTES, &map_k, full0 + 8 * s, 64, row);
+                    tma_load_2d(dst + 2 * DT_HALF_BYTES, &map_v, full0 + 8 * s, 0, row);
+                    tma_load_2d(dst + 3 * DT_HALF_BYTES, &map_v, full0 + 8 * s, 64, row);
                 }
             }
         }
