@@ -17,13 +17,39 @@ _TARGET_CTAS = NUM_SMS * 2
 _CHUNK = 64
 
 
-def decode_splits(rows: int, num_kv_heads: int, key_bound: int) -> int:
-    """Splits of the key range so that rows * kv heads * splits CTAs fill the GPU in one wave
-    (two CTAs of the decode kernel fit on an SM), never more CTAs than that.  ``key_bound``
-    bounds the keys any row reads; it changes only with the table stride, so a captured step
-    keeps its grid."""
-    ctas = max(1, rows * num_kv_heads)
-    return max(1, min(_TARGET_CTAS // ctas, -(-key_bound // _CHUNK), 32))
+# What the split choice assumes of the decode kernel on this GPU (measured: 10 to 128 rows of 8 kv
+# heads at contexts 1,024 to 16,384, 1 to 8 splits each): one CTA streams its keys and values at
+# about 35 GB/s at most (three stages of 32 KB in flight), all CTAs together at the memory's 6.5
+# TB/s, a wave of CTAs costs about 2 us beyond its streaming, the merge pass about 3 us.
+_CTA_GBS, _HBM_GBS, _WAVE_US, _MERGE_US = 35.0, 6500.0, 2.0, 3.0
+
+
+def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int = 128) -> int:
+    """Splits of the key range.  ``key_bound`` bounds the keys any row reads; it changes only with
+    the table stride, so a captured step keeps its grid.
+
+    Two CTAs of the decode kernel fit on an SM: 296 run at a time, in waves.  A CTA is bound by
+    its own streaming rate, a full wave by the memory.  So few (row, kv head) pairs want many
+    splits (more CTAs in flight); a count just above a multiple of 296 wants splits too (a last
+    wave of few long CTAs takes as long as one CTA takes alone: 40 rows of 8 kv heads, unsplit,
+    take 149 us against 123 us in three splits); a count that fills its last wave well wants
+    none.  The splits with the least estimated time are taken."""
+    pairs = max(1, rows * num_kv_heads)
+    most = max(1, min(-(-key_bound // _CHUNK), 32))
+    pair_kb = key_bound * head_dim * 4 / 1e3                         # K and V of one pair, bfloat16, in KB
+    best, best_us = 1, None
+    for s in range(1, most + 1):
+        kb = pair_kb / s
+        alone_us = kb / _CTA_GBS                                     # KB / (GB/s) = us
+        full, rest = divmod(pairs * s, _TARGET_CTAS)
+        us = full * (max(alone_us, _TARGET_CTAS * kb / _HBM_GBS) + _WAVE_US)
+        if rest:
+            us += max(alone_us, rest * kb / _HBM_GBS) + _WAVE_US
+        if s > 1:
+            us += _MERGE_US
+        if best_us is None or us <= best_us + 1e-9:                  # equal estimates: more CTAs in flight
+            best, best_us = s, us
+    return best
 
 
 def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, d: int, scale: float,
