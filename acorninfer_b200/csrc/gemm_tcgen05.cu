@@ -8,7 +8,7 @@
 // ring of shared-memory stages (128-byte swizzle, K-major); one elected thread issues four
 // tcgen05.mma (M=128, N=MB, K=16) per stage into a [128 lanes x MB columns] float32 accumulator
 // in tensor memory; tcgen05.commit frees the stage.  When the K range is split (SPLITS > 1, tiles
-// of up to 32 tokens) the CTAs of one output tile form a thread-block cluster, each reduces its
+// of up to 64 tokens) the CTAs of one output tile form a thread-block cluster, each reduces its
 // share of K, and the partial tiles are exchanged by rows through distributed shared memory:
 // every CTA reads its accumulator with tcgen05.ld (lane = output column) and stores each row
 // into the CTA that finishes it, which adds the partial rows in rank order (deterministic, no
@@ -175,12 +175,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     // memory straight into the receive buffers of their owners (remote shared-memory stores, which
     // do not wait), the cluster meets once, and each CTA adds up, in rank order, the partial rows
     // it received: recv[q][i][128] is row rank + i * csize as computed by rank q.  For tiles of up
-    // to 32 tokens the buffer lies outside the ring, because a peer may still be in its main loop
+    // to 64 tokens the buffer lies outside the ring, because a peer may still be in its main loop
     // when rows arrive; larger tiles are never split and use the drained ring.
     constexpr int RED_FLOATS = 4 * MB > TC_THREADS ? 4 * MB : TC_THREADS;
     float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // reduction scratch, then inv[MB]
     float* inv_s = red + RED_FLOATS;
-    float* recv = MB <= 32 ? inv_s + MB : reinterpret_cast<float*>(smem);
+    float* recv = MB <= 64 ? inv_s + MB : reinterpret_cast<float*>(smem);
     int rank = 0, csize = 1;
     if (splits > 1) {
         cg::cluster_group cluster = cg::this_cluster();
@@ -240,7 +240,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
 #pragma unroll
         for (int i = 0; i < MAX_ROWS; ++i) {
             const int m = rank + i * csize;
-            r_old[i] = (m < m_valid && n_ok) ? ld_global_now(p.resid + (int64_t)(m0 + m) * p.ldr + n0 + col) : 0.f;
+            if (m >= m_valid) break;                                  // the rows of this CTA come first
+            r_old[i] = n_ok ? ld_global_now(p.resid + (int64_t)(m0 + m) * p.ldr + n0 + col) : 0.f;
         }
     }
     if (splits > 1) cg::this_cluster().sync();
@@ -281,20 +282,20 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         float sq[MAX_ROWS];
 #pragma unroll
         for (int i = 0; i < MAX_ROWS; ++i) {
-            sq[i] = 0.f;
             const int m = rank + i * csize;
-            if (m < m_valid) {
-                const float val = tile_sum(i, col) * inv_s[m];
-                if (n_ok) {
-                    const float r = r_old[i] + val;
-                    p.resid[(int64_t)(m0 + m) * p.ldr + n0 + col] = r;
-                    reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + n0 + col] = __float2bfloat16_rn(r * nw);
-                    sq[i] = r * r;
-                }
+            if (m >= m_valid) break;
+            sq[i] = 0.f;
+            const float val = tile_sum(i, col) * inv_s[m];
+            if (n_ok) {
+                const float r = r_old[i] + val;
+                p.resid[(int64_t)(m0 + m) * p.ldr + n0 + col] = r;
+                reinterpret_cast<bf16*>(p.out)[(int64_t)(m0 + m) * p.ldo + n0 + col] = __float2bfloat16_rn(r * nw);
+                sq[i] = r * r;
             }
         }
 #pragma unroll
         for (int i = 0; i < MAX_ROWS; ++i) {
+            if (rank + i * csize >= m_valid) break;
             const float t = warp_sum(sq[i]);
             if (lane == 0) red[warp * MB + i] = t;
         }
@@ -322,7 +323,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
     const size_t ring = (size_t)STAGES * STAGE_BYTES;
     const size_t part = (size_t)MB * TC_BM * sizeof(float);
-    const size_t recv = MB <= 32 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
+    const size_t recv = MB <= 64 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
     const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 +
                         ((4 * MB > TC_THREADS ? 4 * MB : TC_THREADS) + MB) * sizeof(float) + recv + 1024;
     static bool configured = false;
@@ -373,7 +374,7 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
     p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.ss_out = ss_out;
     if (splits > p.kblocks) splits = p.kblocks;
     const int mb = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    if (mb > 32) splits = 1;               // K is split only for tiles of up to 32 tokens
+    if (mb > 64) splits = 1;               // K is split only for tiles of up to 64 tokens
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, ldw, TC_BK, TC_BM);
     if (rc) return rc;
@@ -382,7 +383,7 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
     switch (mb) {
         case 16: return launch_tc<16, 5>(mw, mx, p, splits, stream);     // two CTAs to an SM: about 105 KB each
         case 32: return launch_tc<32, 4>(mw, mx, p, splits, stream);
-        case 64: return launch_tc<64, 4>(mw, mx, p, splits, stream);
+        case 64: return launch_tc<64, 3>(mw, mx, p, splits, stream);
         default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
     }
 }
