@@ -359,7 +359,7 @@ extern "C" int acorn_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int64_t 
 
 // mode, ss_in .. ss_out: see TcParams.  Modes other than plain, and ss_in, are for at most 64 rows.
 extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
-                                int N, int K, int out_f32, int splits, int mode, const float* ss_in, int ss_parts,
+                                int N, int K, int out_f32, int splits, int per_sm, int mode, const float* ss_in, int ss_parts,
                                 int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
                                 float* ss_out, cudaStream_t stream) {
     if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
@@ -380,9 +380,12 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
     if (rc) return rc;
     rc = make_map(&mx, x, M, K, ldx, TC_BK, mb);
     if (rc) return rc;
+    // per_sm: CTAs that fit on an SM together (2 or 3), bought with the depth of the ring; up to 32
+    // tokens only.  Three short rings on an SM stream as well as two long ones and balance better
+    // when the tiles do not share out evenly over the SMs.
     switch (mb) {
-        case 16: return launch_tc<16, 5>(mw, mx, p, splits, stream);     // two CTAs to an SM: about 105 KB each
-        case 32: return launch_tc<32, 4>(mw, mx, p, splits, stream);
+        case 16: return per_sm == 3 ? launch_tc<16, 3>(mw, mx, p, splits, stream) : launch_tc<16, 5>(mw, mx, p, splits, stream);
+        case 32: return per_sm == 3 ? launch_tc<32, 2>(mw, mx, p, splits, stream) : launch_tc<32, 4>(mw, mx, p, splits, stream);
         case 64: return launch_tc<64, 3>(mw, mx, p, splits, stream);
         default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
     }
@@ -390,7 +393,7 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
 
 extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
                              int N, int K, int out_f32, int splits, cudaStream_t stream) {
-    return acorn_gemm_tc_ex(x, ldx, w, ldw, out, ldo, M, N, K, out_f32, splits, TC_MODE_PLAIN, nullptr, 0, 0, 0.f,
+    return acorn_gemm_tc_ex(x, ldx, w, ldw, out, ldo, M, N, K, out_f32, splits, 2, TC_MODE_PLAIN, nullptr, 0, 0, 0.f,
                             nullptr, 0, nullptr, nullptr, stream);
 }
 

@@ -51,7 +51,7 @@ def bench_gemm(a) -> None:
     copies = max(2, int(400e6 // (a.n * a.k * 2)) + 1)
     ws = [torch.randn(a.n, a.k, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     x = torch.randn(a.m, a.k, device=DEV, dtype=torch.bfloat16)
-    splits = a.splits or ops.gemm_tc_splits(a.m, a.n, a.k)
+    splits, per_sm = (a.splits, a.per_sm) if a.splits else ops.gemm_tc_plan(a.m, a.n, a.k)
     resid = torch.randn(a.m, a.n, device=DEV)
     norm_w = torch.ones(a.n, device=DEV)
     xin = x
@@ -59,10 +59,10 @@ def bench_gemm(a) -> None:
         xin = ops.NormedRows(x, torch.rand(32, a.m, device=DEV) + 1.0, 1e-6, a.k)
     ep = ops.AddNormEpilogue(resid, norm_w, 1e-6) if a.epilogue == "add_norm" else None
     us = _time([lambda w=w: ops.gemm_tc(xin, w, torch.bfloat16, splits=splits, epilogue=ep,
-                                        swiglu=a.epilogue == "swiglu") for w in ws], a.reps, a.graph)
+                                        swiglu=a.epilogue == "swiglu", per_sm=per_sm) for w in ws], a.reps, a.graph)
     lib = _time([lambda w=w: torch.mm(x, w.t()) for w in ws], a.reps, a.graph) if a.library else float("nan")
     gb, fl = a.n * a.k * 2 / 1e9, 2.0 * a.m * a.n * a.k
-    print(f"gemm_tcgen05 M={a.m} N={a.n} K={a.k} splits={splits} epilogue={a.epilogue} normed={a.normed}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of weights, "
+    print(f"gemm_tcgen05 M={a.m} N={a.n} K={a.k} splits={splits} per_sm={per_sm} epilogue={a.epilogue} normed={a.normed}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of weights, "
           f"{fl / us / 1e6:.1f} TFLOPS; library product {lib:.1f} us; error flag {ops.gemm_tc_error()}")
 
 
@@ -169,6 +169,7 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=24576)
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--splits", type=int, default=0)
+    g.add_argument("--per-sm", type=int, default=2, help="with --splits: CTAs to an SM (2: deep ring, 3: short ring)")
     g.add_argument("--library", type=int, default=1, help="also time the library product")
     g.add_argument("--epilogue", default="none", choices=["none", "add_norm", "swiglu"])
     g.add_argument("--normed", type=int, default=0, help="1: x is NormedRows (row factors applied in the epilogue)")

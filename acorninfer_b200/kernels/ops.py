@@ -114,7 +114,7 @@ class _Sigs:
     acorn_attention_prefill_tc_supported = [c_int, c_int, c_int, c_int]
     acorn_attention_tc_error = []
     acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
-                        c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+                        c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
     acorn_gemm_tc_error = []
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
@@ -486,15 +486,29 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and bool(lib().acorn_gemm_tc_supported(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))))
 
 
-def gemm_tc_splits(M: int, N: int, K: int) -> int:
-    """Split of the K range (a cluster of that many CTAs per output tile): a power of two, at most
-    8, chosen so that a matrix with few 128-row tiles still puts one to two CTAs on every SM."""
-    tiles = -(-N // 128) * -(-M // (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128))
+def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int]:
+    """(splits of the K range, CTAs to an SM) for a product on the tcgen05 kernel.
+
+    Splits: a cluster of that many CTAs per output tile, a power of two, at most 8, chosen so that a
+    matrix with few 128-row tiles still puts one to two CTAs on every SM.  CTAs to an SM: two, with
+    a deep ring, or three with a short one (up to 32 rows).  An SM takes in about 66 GB/s, so the SM
+    with the most tiles sets the time: 192 tiles on 148 SMs leave 44 SMs with two tiles (2.0 tiles'
+    worth), while 384 half tiles, three to an SM, leave none with more than three halves (1.5).  The
+    second form is taken for unsplit matrices with 1 to 1.5 tiles to an SM; where K is split
+    already it gained nothing."""
+    rows = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = -(-N // 128) * -(-M // rows)
     kblocks = -(-K // 64)
     splits = 1
     while splits < 8 and tiles * splits * 2 <= 2 * 148 and kblocks // (splits * 2) >= 4:
         splits *= 2
-    return splits
+    if rows <= 32 and splits == 1 and kblocks >= 8 and 148 < tiles and tiles * 2 <= 3 * 148:
+        return 2, 3                     # more tiles than SMs, fewer than 1.5 to an SM (measured: 36.0 -> 33.3 us)
+    return splits, 2
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    return gemm_tc_plan(M, N, K)[0]
 
 
 # At or below this many rows the tcgen05 kernel (weights on the 128-row side of the MMA) streams the
@@ -525,7 +539,8 @@ class AddNormEpilogue:
 
 
 def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
-            out: torch.Tensor | None = None, epilogue: AddNormEpilogue | None = None, swiglu: bool = False):
+            out: torch.Tensor | None = None, epilogue: AddNormEpilogue | None = None, swiglu: bool = False,
+            per_sm: int = 2):
     """x [M, K] @ w [N, K]^T on tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
     ``x`` may be ``NormedRows`` (at most 64 rows): the rows' RMS factors are applied to the product.
@@ -543,7 +558,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
     if (rows is not None or epilogue is not None or swiglu) and M > 64:
         raise KernelError(f"gemm_tc: fused norm / SwiGLU epilogues take at most 64 rows, got {M}")
     if splits is None:
-        splits = gemm_tc_splits(M, N, K)
+        splits, per_sm = gemm_tc_plan(M, N, K)
     mode, resid, ldr, norm_w, ss_out = 0, None, 0, None, None
     out_cols = N
     if epilogue is not None:
@@ -564,7 +579,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
     _check(out, "out", out_dtype, 2)
     _ok(lib().acorn_gemm_tc_ex(
         xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
-        1 if out_dtype == torch.float32 else 0, int(splits), mode,
+        1 if out_dtype == torch.float32 else 0, int(splits), int(per_sm), mode,
         rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
         rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
         _ptr(resid), ldr, _ptr(norm_w), _ptr(ss_out), _stream()), "gemm_tc")
