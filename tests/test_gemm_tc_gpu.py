@@ -31,6 +31,20 @@ def test_gemm_tc_matches_float32(M, N, K, splits, out_dtype):
     assert torch.equal(out, ops().gemm_tc(x, w, out_dtype, splits=splits))      # deterministic
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(3, 500, 512, 2), (16, 128, 4096, 8), (29, 333, 1000, 3), (32, 40, 256, 1)])
+def test_gemm_tc_three_ctas_to_an_sm(M, N, K, splits):
+    """The form with short rings (three CTAs fit on an SM) gives the same product."""
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = torch.randn(N, K, device=DEV).to(torch.bfloat16)
+    out = ops().gemm_tc(x, w, torch.float32, splits=splits, per_sm=3)
+    assert ops().gemm_tc_error() == 0
+    assert torch.allclose(out.double(), x.double() @ w.double().T, atol=1e-3 * K ** 0.5, rtol=1e-4)
+    assert torch.equal(out, ops().gemm_tc(x, w, torch.float32, splits=splits, per_sm=2))     # same order of sums
+    # the plan takes that form for a matrix with more tiles than SMs and fewer than 1.5 to an SM
+    assert ops().gemm_tc_plan(8, 24576, 4096) == (2, 3) and ops().gemm_tc_plan(8, 4096, 4096)[1] == 2
+
+
 def test_gemm_tc_strided_operands_and_refusals():
     from acorninfer_b200.kernels.ops import KernelError
     big = torch.randn(40, 512, device=DEV).to(torch.bfloat16)
