@@ -35,6 +35,9 @@ __device__ int g_gemm_tc_error = 0;
 #define TC_MODE_PLAIN 0       // out = product
 #define TC_MODE_ADD_NORM 1    // residual += product; out = bf16(residual * norm_w); ss_out = partial sum of squares
 #define TC_MODE_SWIGLU 2      // tiles of 64 gate + 64 up columns: out = silu(gate) * up
+#define TC_MODE_QKV_ROPE 3    // tiles are heads of 128: q/k RMSNorm + rotation; k and v to their cache pages
+// reduction scratch of the epilogues (floats): four partial sums a row, or a head and its partial sums
+#define TC_RED_FLOATS(MB) (4 * (MB) > 256 ? 4 * (MB) : 256)
 
 struct TcParams {
     void* out;
@@ -52,6 +55,19 @@ struct TcParams {
     int64_t ldr;
     const float* norm_w;     // [N]
     float* ss_out;           // [ceil(N / 128), M]
+    // TC_MODE_QKV_ROPE: W rows are nq query heads, nkv key heads, nkv value heads of 128; out takes
+    // the query heads (row stride ldo), the cache pages [page, nkv, P, 128] the others
+    const int* positions;    // [M]
+    const int* token_row;    // [M] row of the block table
+    const int* block_table;
+    const int* page_base;
+    const float* q_w;        // [128] or nullptr: no norm
+    const float* k_w;
+    const float* inv_freq;   // [64]
+    bf16* k_pages;
+    bf16* v_pages;           // nullptr: keys and values are not written (a layer that reads another's cache)
+    int table_stride, nq, nkv, logP;
+    float rope_eps;
 };
 
 // A load that the compiler leaves where it is written (it may not sink it below a barrier to the
@@ -177,7 +193,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     // it received: recv[q][i][128] is row rank + i * csize as computed by rank q.  For tiles of up
     // to 64 tokens the buffer lies outside the ring, because a peer may still be in its main loop
     // when rows arrive; larger tiles are never split and use the drained ring.
-    constexpr int RED_FLOATS = 4 * MB > TC_THREADS ? 4 * MB : TC_THREADS;
+    constexpr int RED_FLOATS = TC_RED_FLOATS(MB);
     float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // reduction scratch, then inv[MB]
     float* inv_s = red + RED_FLOATS;
     float* recv = MB <= 64 ? inv_s + MB : reinterpret_cast<float*>(smem);
@@ -276,6 +292,47 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
                         __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
             }
         }
+    } else if (p.mode == TC_MODE_QKV_ROPE) {
+        // The tile is one head.  Query and key heads: RMSNorm over the head (float32, on the
+        // accumulator: no rounding in between), then the rotation of (x[j], x[j + 64]) by
+        // position * inv_freq[j]; keys and values go to the token's slot of its cache page.
+        const int head = blockIdx.x;
+        const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+        const int kvh = is_q ? 0 : (head - p.nq) % p.nkv;
+        const float* hw = is_q ? p.q_w : p.k_w;
+        const float wcol = ((is_q || is_k) && hw != nullptr) ? hw[col] : 1.f;
+        const float freq = p.inv_freq[col & 63];
+        float* xch = red;                                             // [4] partial sums, then [128] the head
+        for (int i = 0, m = rank; m < m_valid; ++i, m += csize) {
+            float val = tile_sum(i, col) * inv_s[m];
+            const int t = m0 + m, pos = p.positions[t];
+            if (is_q || is_k) {
+                if (hw != nullptr) {
+                    const float part = warp_sum(val * val);
+                    __syncthreads();                                  // the row before has been read
+                    if (lane == 0) xch[warp] = part;
+                    __syncthreads();
+                    val = val * rsqrtf((xch[0] + xch[1] + xch[2] + xch[3]) / (float)TC_BM + p.rope_eps) * wcol;
+                } else {
+                    __syncthreads();
+                }
+                xch[4 + col] = val;
+                __syncthreads();
+                const float other = xch[4 + (col ^ 64)];
+                float sn, cs;
+                sincosf((float)pos * freq, &sn, &cs);
+                val = col < 64 ? val * cs - other * sn : val * cs + other * sn;
+            }
+            if (is_q) {
+                reinterpret_cast<bf16*>(p.out)[(int64_t)t * p.ldo + head * TC_BM + col] = __float2bfloat16_rn(val);
+            } else if (p.v_pages != nullptr) {
+                const int r = p.token_row[t];
+                const int page = p.block_table[(int64_t)r * p.table_stride + (pos >> p.logP) - p.page_base[r]];
+                bf16* dst = (is_k ? p.k_pages : p.v_pages) +
+                            ((((int64_t)page * p.nkv + kvh) << p.logP) + (pos & ((1 << p.logP) - 1))) * TC_BM + col;
+                *dst = __float2bfloat16_rn(val);
+            }
+        }
     } else {
         // TC_MODE_ADD_NORM: residual += product; out = bf16(residual * norm weight), not yet
         // scaled; this tile's share of sum(residual^2) per row goes to ss_out[tile][row]
@@ -325,7 +382,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     const size_t part = (size_t)MB * TC_BM * sizeof(float);
     const size_t recv = MB <= 64 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
     const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 +
-                        ((4 * MB > TC_THREADS ? 4 * MB : TC_THREADS) + MB) * sizeof(float) + recv + 1024;
+                        (TC_RED_FLOATS(MB) + MB) * sizeof(float) + recv + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MB, STAGES>,
@@ -357,21 +414,14 @@ extern "C" int acorn_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int64_t 
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && M <= (1 << 30);
 }
 
-// mode, ss_in .. ss_out: see TcParams.  Modes other than plain, and ss_in, are for at most 64 rows.
-extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
-                                int N, int K, int out_f32, int splits, int per_sm, int mode, const float* ss_in, int ss_parts,
-                                int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
-                                float* ss_out, cudaStream_t stream) {
+static int run_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, TcParams& p, int splits, int per_sm,
+                  cudaStream_t stream) {
+    const int M = p.M, N = p.N, K = p.K;
     if (!acorn_gemm_tc_supported(M, N, K, ldx, ldw) || splits < 1 || splits > 8) return ACORN_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACORN_ERR_UNSUPPORTED;
-    if (mode != TC_MODE_PLAIN && (M > 64 || out_f32)) return ACORN_ERR_UNSUPPORTED;
-    if (mode == TC_MODE_SWIGLU && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
-    if (mode == TC_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
-    if (ss_in != nullptr && (M > 64 || ss_parts < 1 || norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
-    TcParams p;
-    p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.kblocks = (K + TC_BK - 1) / TC_BK; p.out_f32 = out_f32;
-    p.mode = mode; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_width = norm_width; p.eps = eps;
-    p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.ss_out = ss_out;
+    if (p.mode != TC_MODE_PLAIN && (M > 64 || p.out_f32)) return ACORN_ERR_UNSUPPORTED;
+    if (p.ss_in != nullptr && (M > 64 || p.ss_parts < 1 || p.norm_width < 1)) return ACORN_ERR_UNSUPPORTED;
+    p.kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits > p.kblocks) splits = p.kblocks;
     const int mb = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     if (mb > 64) splits = 1;               // K is split only for tiles of up to 64 tokens
@@ -389,6 +439,43 @@ extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64
         case 64: return launch_tc<64, 3>(mw, mx, p, splits, stream);
         default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
     }
+}
+
+// mode, ss_in .. ss_out: see TcParams.  Modes other than plain, and ss_in, are for at most 64 rows.
+extern "C" int acorn_gemm_tc_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,
+                                int N, int K, int out_f32, int splits, int per_sm, int mode, const float* ss_in, int ss_parts,
+                                int norm_width, float eps, float* resid, int64_t ldr, const float* norm_w,
+                                float* ss_out, cudaStream_t stream) {
+    if (mode != TC_MODE_PLAIN && mode != TC_MODE_ADD_NORM && mode != TC_MODE_SWIGLU) return ACORN_ERR_UNSUPPORTED;
+    if (mode == TC_MODE_SWIGLU && N % 128 != 0) return ACORN_ERR_UNSUPPORTED;
+    if (mode == TC_MODE_ADD_NORM && (resid == nullptr || norm_w == nullptr || ss_out == nullptr)) return ACORN_ERR_UNSUPPORTED;
+    TcParams p = {};
+    p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
+    p.mode = mode; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_width = norm_width; p.eps = eps;
+    p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.ss_out = ss_out;
+    return run_tc(x, ldx, w, ldw, p, splits, per_sm, stream);
+}
+
+// The q/k/v product of an attention layer with head size 128 (TC_MODE_QKV_ROPE): w is [(nq + 2 nkv)
+// * 128, K]; out [M, ldo] takes the query heads; k_pages / v_pages ([pages, nkv, P, 128], P a power
+// of two) the keys and values, or nothing when they are nullptr.
+extern "C" int acorn_gemm_tc_qkv_rope(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo,
+                                      int M, int K, int splits, int per_sm, const float* ss_in, int ss_parts,
+                                      int norm_width, float eps, const int* positions, const int* token_row,
+                                      const int* block_table, const int* page_base, int table_stride, void* k_pages,
+                                      void* v_pages, const float* q_w, const float* k_w, const float* inv_freq, int nq,
+                                      int nkv, int P, float rope_eps, cudaStream_t stream) {
+    const int logP = acorn_log2_exact_tc(P);
+    if (nq < 1 || nkv < 1 || logP < 0 || positions == nullptr || inv_freq == nullptr) return ACORN_ERR_UNSUPPORTED;
+    if ((k_pages == nullptr) != (v_pages == nullptr)) return ACORN_ERR_UNSUPPORTED;
+    if (k_pages != nullptr && (token_row == nullptr || block_table == nullptr || page_base == nullptr)) return ACORN_ERR_UNSUPPORTED;
+    TcParams p = {};
+    p.out = out; p.ldo = ldo; p.M = M; p.N = (nq + 2 * nkv) * TC_BM; p.K = K; p.out_f32 = 0;
+    p.mode = TC_MODE_QKV_ROPE; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_width = norm_width; p.eps = eps;
+    p.positions = positions; p.token_row = token_row; p.block_table = block_table; p.page_base = page_base;
+    p.table_stride = table_stride; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages; p.q_w = q_w; p.k_w = k_w;
+    p.inv_freq = inv_freq; p.nq = nq; p.nkv = nkv; p.logP = logP; p.rope_eps = rope_eps;
+    return run_tc(x, ldx, w, ldw, p, splits, per_sm, stream);
 }
 
 extern "C" int acorn_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int M,

@@ -115,6 +115,9 @@ class _Sigs:
     acorn_attention_tc_error = []
     acorn_gemm_tc_ex = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                         c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+    acorn_gemm_tc_qkv_rope = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                              c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
     acorn_gemm_tc_error = []
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
@@ -536,6 +539,74 @@ class AddNormEpilogue:
     resid32: torch.Tensor
     weight32: torch.Tensor
     eps: float
+
+
+@dataclass
+class RopeKvEpilogue:
+    """What the q/k/v product of an attention layer with head size 128 does with its result instead of
+    writing it: per-head RMSNorm of the query and key heads (weights or None), rotation of the whole
+    head in half pairing by ``position * inv_freq``, query heads to the output, keys and values to the
+    token's slot in its cache pages (``k_pages`` None: they are dropped).  The same arithmetic as
+    ``qk_rope_kv`` after a plain product, without the bfloat16 rounding in between."""
+
+    positions: torch.Tensor
+    token_row: torch.Tensor
+    block_table: torch.Tensor
+    page_base: torch.Tensor
+    k_pages: torch.Tensor | None
+    v_pages: torch.Tensor | None
+    q_weight32: torch.Tensor | None
+    k_weight32: torch.Tensor | None
+    inv_freq: torch.Tensor
+    num_heads: int
+    num_kv_heads: int
+    eps: float
+
+
+def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The q/k/v product with ``RopeKvEpilogue``: returns [M, (nq + 2 nkv) * 128] bfloat16 whose first
+    nq * 128 columns hold the finished query heads (the others are not written)."""
+    rows = x if isinstance(x, NormedRows) else None
+    xt = rows.x if rows is not None else x
+    nq, nkv = ep.num_heads, ep.num_kv_heads
+    M, K = xt.shape
+    N = (nq + 2 * nkv) * 128
+    if not gemm_tc_supported(xt, w) or w.shape[0] != N or M > GEMM_TC_MAX_ROWS:
+        raise KernelError(f"gemm_tc_qkv_rope does not take x {tuple(xt.shape)} {xt.dtype}, w {tuple(w.shape)} {w.dtype} "
+                          f"for {nq}/{nkv} heads of 128 (at most {GEMM_TC_MAX_ROWS} rows)")
+    _check(ep.positions, "positions", torch.int32, 1)
+    _check(ep.inv_freq, "inv_freq", torch.float32, 1)
+    if ep.inv_freq.numel() != 64 or ep.positions.numel() < M:
+        raise KernelError("gemm_tc_qkv_rope: inv_freq must have 64 entries and positions one per row")
+    P = 1
+    if ep.k_pages is not None:
+        _check(ep.k_pages, "k_pages", torch.bfloat16, 4)
+        _check(ep.v_pages, "v_pages", torch.bfloat16, 4)
+        _check(ep.block_table, "block_table", torch.int32, 2)
+        if tuple(ep.k_pages.shape[1:]) != (nkv, ep.k_pages.shape[2], 128) or ep.v_pages.shape != ep.k_pages.shape:
+            raise KernelError("gemm_tc_qkv_rope: cache pages must be [pages, nkv, P, 128]")
+        P = ep.k_pages.shape[2]
+    for wt in (ep.q_weight32, ep.k_weight32):
+        if wt is not None:
+            _check(wt, "head norm weight", torch.float32, 1)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=xt.device)
+    _check(out, "out", torch.bfloat16, 2)
+    splits, per_sm = gemm_tc_plan(M, N, K)
+    _ok(lib().acorn_gemm_tc_qkv_rope(
+        xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, K, splits, per_sm,
+        rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
+        rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
+        ep.positions.data_ptr(), _ptr(ep.token_row), _ptr(ep.block_table), _ptr(ep.page_base),
+        ep.block_table.stride(0) if ep.block_table is not None else 0, _ptr(ep.k_pages), _ptr(ep.v_pages),
+        _ptr(ep.q_weight32), _ptr(ep.k_weight32), ep.inv_freq.data_ptr(), nq, nkv, P, float(ep.eps), _stream()),
+        "gemm_tc_qkv_rope")
+    return out
+
+
+def rope_kv_fusable(num_rows: int, dtype: torch.dtype, head_dim: int, rotary_dim: int, interleaved: bool) -> bool:
+    """Whether the q/k/v product of such a layer can take ``RopeKvEpilogue`` for this many rows."""
+    return fused_rows_ok(num_rows, dtype) and head_dim == 128 and rotary_dim == 128 and not interleaved
 
 
 def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,

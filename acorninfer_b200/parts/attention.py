@@ -75,14 +75,25 @@ class Attention(Mixer):
 
     def forward(self, x, inputs, cache, epilogue=None):
         g = inputs.groups[cache.group]
-        qkv = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
         pos = self.position
-        ops.qk_rope_kv(qkv, self.q_norm32, self.k_norm32,
-                       pos.inv_freq if pos is not None else _no_freq(self.ctx.device),
-                       inputs.positions, inputs.token_row, g.block_table, g.page_base,
-                       cache.k_pages, cache.v_pages, self.nq, self.nkv, self.d,
-                       pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
-                       self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write)
+        rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
+        if (pos is not None and self.w_qkv.dtype == torch.bfloat16 and ops.gemm_tc_supported(
+                x.x if isinstance(x, ops.NormedRows) else x, self.w_qkv)
+                and ops.rope_kv_fusable(rows, self.ctx.dtype, self.d, pos.rotary_dim, pos.interleaved)):
+            # few rows, head size 128: norm, rotation and the cache write are the epilogue of the product
+            qkv = ops.gemm_tc_qkv_rope(x, self.w_qkv, ops.RopeKvEpilogue(
+                inputs.positions, inputs.token_row, g.block_table, g.page_base,
+                cache.k_pages if cache.write else None, cache.v_pages if cache.write else None,
+                self.q_norm32, self.k_norm32, pos.inv_freq, self.nq, self.nkv,
+                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0))
+        else:
+            qkv = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
+            ops.qk_rope_kv(qkv, self.q_norm32, self.k_norm32,
+                           pos.inv_freq if pos is not None else _no_freq(self.ctx.device),
+                           inputs.positions, inputs.token_row, g.block_table, g.page_base,
+                           cache.k_pages, cache.v_pages, self.nq, self.nkv, self.d,
+                           pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
+                           self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write)
         out = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window)
         return ops.linear(out, self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue)
 

@@ -102,3 +102,50 @@ def test_gemm_tc_swiglu_epilogue(M, I, K, splits):
     gu = ops().gemm_tc(x, w, torch.bfloat16, splits=1)
     assert torch.allclose(ops().swiglu(gu, block=64).float(), out.float(), atol=2e-2, rtol=2e-2)
     assert ops().gemm_tc_error() == 0
+
+
+@pytest.mark.parametrize("nq,nkv,K,qlens,norm,write", [(4, 2, 256, [7, 1, 5], True, True), (6, 1, 520, [1, 1, 1, 1], True, True),
+                                                       (2, 2, 128, [30], False, True), (8, 4, 1024, [3, 20], True, False)])
+def test_gemm_tc_qkv_rope_epilogue(nq, nkv, K, qlens, norm, write):
+    """The q/k/v product with norm, rotation and cache write as its epilogue, against the plain
+    product followed by the stand-alone kernel (which rounds to bfloat16 in between)."""
+    from acorninfer_b200.kernels.ops import RopeKvEpilogue
+    from tests.paged import rows_layout
+    torch.manual_seed(nq * 10 + nkv)
+    d, P, NP, eps, theta = 128, 16, 300, 3e-6, 1e4
+    befores = [0, 37, 4000, 15][:len(qlens)]
+    lay = rows_layout(befores, qlens, P, NP, seed=2)
+    T = lay["num_tokens"]
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    qw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    inv = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    # reference: the two kernels one after the other
+    ref = ops().gemm_tc(x, w, torch.bfloat16)
+    k_ref = torch.zeros(NP, nkv, P, d, device=DEV, dtype=torch.bfloat16)
+    v_ref = torch.zeros_like(k_ref)
+    ops().qk_rope_kv(ref, qw, kw, inv, lay["positions"], lay["token_row"], lay["block_table"], lay["page_base"],
+                     k_ref, v_ref, nq, nkv, d, d, False, eps)
+    k_pages, v_pages = torch.zeros_like(k_ref), torch.zeros_like(k_ref)
+    out = ops().gemm_tc_qkv_rope(x, w, RopeKvEpilogue(
+        lay["positions"], lay["token_row"], lay["block_table"], lay["page_base"], k_pages if write else None,
+        v_pages if write else None, qw, kw, inv, nq, nkv, eps))
+    assert ops().gemm_tc_error() == 0
+    tol = dict(atol=4e-2, rtol=2e-2)
+    assert torch.allclose(out[:, :nq * d].float(), ref[:, :nq * d].float(), **tol)
+    if write:
+        assert torch.allclose(k_pages.float(), k_ref.float(), **tol)
+        assert torch.allclose(v_pages.float(), v_ref.float(), **tol)
+        assert float(k_pages.float().abs().sum()) > 0
+    else:
+        assert float(k_pages.float().abs().sum()) == 0 and float(v_pages.float().abs().sum()) == 0
+    # against float64 arithmetic for the query heads: norm and rotation of the exact product
+    q = (x.double() @ w.double().T)[:, :nq * d].view(T, nq, d).cpu()
+    if norm:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * qw.double().cpu()
+    ang = lay["positions"].cpu().double()[:, None] * inv.cpu().double()[None, :]
+    c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = q[..., :64], q[..., 64:]
+    want = torch.cat([a * c - b * s_, b * c + a * s_], dim=-1).reshape(T, nq * d)
+    assert torch.allclose(out[:, :nq * d].double().cpu(), want, atol=3e-2, rtol=2e-2)

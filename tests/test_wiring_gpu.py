@@ -37,8 +37,9 @@ def test_head_size_128_takes_the_tcgen05_and_tma_kernels(tmp_path):
     # two decoded tokens: TMA decode kernel, tcgen05 products with fused epilogues, no norm kernel between layers
     c = counts_of(lambda: runner.step([StepEntry(a, [3], [0]), StepEntry(b, [4], [0])]))
     assert c.get("attention_decode_tma") == layers and "attention_prefill_tc" not in c and "attention_plain" not in c
-    assert c.get("gemm_tc") == 4 * layers + 1       # qkv, o, gate_up(+SwiGLU), down per layer, and the output matrix
-    assert "swiglu" not in c and c.get("add_rmsnorm") == 2      # first norm and final norm only
+    assert c.get("gemm_tc") == 3 * layers + 1       # o, gate_up(+SwiGLU), down per layer, and the output matrix
+    assert c.get("gemm_tc_qkv_rope") == layers      # q/k-norm, rotation and the cache write ride on the qkv product
+    assert "swiglu" not in c and "qk_rope_kv" not in c and c.get("add_rmsnorm") == 2      # first norm and final norm only
     # a mixed step: the decoded token through the decode kernel, the portion through a prefill kernel
     c = counts_of(lambda: runner.step([StepEntry(a, [5], [0]), StepEntry(b, random_tokens(33, V, 3), [])]))
     assert c.get("attention_decode_tma") == layers and c.get("attention_prefill_tc") == layers
