@@ -670,7 +670,7 @@ def fused_rows_ok(num_rows: int, dtype: torch.dtype) -> bool:
 
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: AddNormEpilogue | None = None,
-           swiglu: bool = False):
+           swiglu: bool = False, residual32: torch.Tensor | None = None):
     """x [T, K] times w [N, K] transposed.
 
     float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
@@ -680,6 +680,9 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
     A weight stored in float32 under a bfloat16 engine is multiplied in float32.
     ``x`` as ``NormedRows``, ``epilogue`` and ``swiglu`` exist on the tcgen05 path only
     (``fused_rows_ok``); asking for them elsewhere is an error, not a silent detour.
+    ``residual32`` ([T, N] float32) is an offer: where the product goes to the library it is
+    added to ``residual32`` in place, in float32 (the library's C operand: the product is not
+    rounded first), and None is returned; elsewhere the offer is ignored and the product returned.
     """
     fused = isinstance(x, NormedRows) or epilogue is not None or swiglu
     xt = x.x if isinstance(x, NormedRows) else x
@@ -696,6 +699,10 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
         raise KernelError(f"linear: unsupported dtypes x={x.dtype}, w={w.dtype}")
     if x.shape[0] <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w):
         return gemm_tc(x, w, out_dtype)
+    if residual32 is not None and residual32.dtype == torch.float32 and residual32.is_contiguous() \
+            and tuple(residual32.shape) == (x.shape[0], w.shape[0]):
+        torch.addmm(residual32, x, w.t(), out_dtype=torch.float32, out=residual32)
+        return None
     if out_dtype == torch.float32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     return torch.mm(x, w.t())

@@ -26,6 +26,7 @@ from .base import MIXERS, BuildContext, CacheNeeds, KVNeeds, Mixer, TensorSpec
 class Attention(Mixer):
     graph_safe = True
     supports_epilogue = True
+    adds_residual = True
 
     def __init__(self, ctx: BuildContext, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: str | None, scale: float, qk_norm_eps: float | None = None,
@@ -73,7 +74,7 @@ class Attention(Mixer):
         return (ops.fused_rows_ok(num_rows, self.ctx.dtype) and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and (self.nq * self.d) % 8 == 0)
 
-    def forward(self, x, inputs, cache, epilogue=None):
+    def forward(self, x, inputs, cache, epilogue=None, residual32=None):
         g = inputs.groups[cache.group]
         pos = self.position
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
@@ -95,7 +96,8 @@ class Attention(Mixer):
                            pos.rotary_dim if pos is not None else 0, pos.interleaved if pos is not None else False,
                            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=cache.write)
         out = attn_kernels.paged_attention(qkv, inputs, g, cache, self.nq, self.nkv, self.d, self.scale, self.window)
-        return ops.linear(out, self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue)
+        return ops.linear(out, self.w_o, out_dtype=self.ctx.dtype, epilogue=epilogue,
+                          residual32=residual32 if epilogue is None else None)
 
 
 _NO_FREQ: dict = {}

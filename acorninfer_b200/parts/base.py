@@ -169,6 +169,9 @@ class Mixer(Part):
     # True: ``forward`` takes ``x`` as ``NormedRows`` and an ``epilogue`` for its last product
     # (see ``kernels.ops.NormedRows`` / ``AddNormEpilogue``) when ``fusable(rows)`` says so.
     supports_epilogue = False
+    # True: ``forward`` takes ``residual32`` (the float32 residual stream) and may add its result to
+    # it in place instead of returning it; it then returns None.
+    adds_residual = False
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds()
@@ -182,6 +185,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     supports_epilogue = False
+    adds_residual = False            # as for mixers
 
     def fusable(self, num_rows: int) -> bool:
         return False

@@ -38,8 +38,15 @@ class PreNormBlock(Block):
         if ep is not None:
             h = self.mixer.forward(h, inputs, cache, epilogue=ep)
         else:
-            h = self.norms["feed_forward"].add_forward(resid32, self.mixer.forward(h, inputs, cache))
+            # a part that can, adds its result to the residual stream itself (delta None)
+            if self.mixer.adds_residual:
+                delta = self.mixer.forward(h, inputs, cache, residual32=resid32)
+            else:
+                delta = self.mixer.forward(h, inputs, cache)
+            h = self.norms["feed_forward"].add_forward(resid32, delta)
         ep = next_norm.as_epilogue(resid32) if (fuse and next_norm is not None) else None
         if ep is not None:
             return resid32, self.feed_forward.forward(h, inputs, epilogue=ep)
+        if self.feed_forward.adds_residual:
+            return resid32, self.feed_forward.forward(h, inputs, residual32=resid32)
         return resid32, self.feed_forward.forward(h, inputs)

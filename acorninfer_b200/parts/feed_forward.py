@@ -15,6 +15,7 @@ from .base import FEED_FORWARDS, BuildContext, FeedForward, TensorSpec
 class SwiGLU(FeedForward):
     graph_safe = True
     supports_epilogue = True
+    adds_residual = True
 
     def __init__(self, ctx: BuildContext, hidden_size: int, intermediate_size: int):
         self.ctx = ctx
@@ -46,11 +47,12 @@ class SwiGLU(FeedForward):
                 and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0)
 
-    def forward(self, x, inputs, epilogue=None):
+    def forward(self, x, inputs, epilogue=None, residual32=None):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
         if self.block == 64 and self.fusable(rows):
             h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True)
         else:
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)
             h = ops.swiglu(gu, block=self.block)
-        return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, epilogue=epilogue)
+        return ops.linear(h, self.w_down, out_dtype=self.ctx.dtype, epilogue=epilogue,
+                          residual32=residual32 if epilogue is None else None)
