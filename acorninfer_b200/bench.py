@@ -7,7 +7,7 @@ has them (``--model-dir --device --num-blocks --page-size --max-running --waterm
 ``RESULT C=... ttft_p50=... tpot_mean=... tok_s=...`` line per concurrency level (``:68-99``).
 
 Added: ``--random-config FILE`` (a config.json: random weights are drawn on the device, no
-model folder needed), ``--dtype``, ``--chunked-budget``, and ``--prompt-range LO HI`` /
+model folder needed) or ``--random-preset NAME`` (the sizes of a published model, e.g. qwen3-8b), ``--dtype``, ``--chunked-budget``, and ``--prompt-range LO HI`` /
 ``--output-range LO HI`` for requests of mixed lengths (the continuous-batching workload:
 all requests arrive at once, prompts and outputs uniform in the ranges).
 """
@@ -22,6 +22,7 @@ import time
 import torch
 
 from .config.model_config import ModelConfig
+from .config.presets import PRESETS, preset
 from .engine.engine import Engine
 from .engine.runner import ModelRunner
 from .registry import config_from_dict
@@ -73,6 +74,7 @@ def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="acorninfer_b200.bench", description=__doc__.split("\n\n")[0])
     p.add_argument("--model-dir", default=None)
     p.add_argument("--random-config", default=None, help="config.json to draw random weights for (no model folder)")
+    p.add_argument("--random-preset", default=None, help="the same from a model's published sizes: " + ", ".join(sorted(PRESETS)))
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--num-blocks", type=int, default=1024)
@@ -87,8 +89,8 @@ def main(argv=None) -> int:
     p.add_argument("--concurrency", type=int, nargs="+", default=[1, 4, 8])
     p.add_argument("--seed", type=int, default=20261027)
     args = p.parse_args(argv)
-    if (args.model_dir is None) == (args.random_config is None):
-        p.error("give exactly one of --model-dir and --random-config")
+    if sum(x is not None for x in (args.model_dir, args.random_config, args.random_preset)) != 1:
+        p.error("give exactly one of --model-dir, --random-config and --random-preset")
 
     kw = dict(dtype=args.dtype, device=args.device, num_blocks=args.num_blocks, page_size=args.page_size,
               max_requests=args.max_running,
@@ -97,8 +99,9 @@ def main(argv=None) -> int:
         print(f"loading {args.model_dir} -> {args.device} ({args.dtype}) ...")
         runner = ModelRunner.from_model_dir(args.model_dir, **kw)
     else:
-        cfg: ModelConfig = config_from_dict(json.loads(open(args.random_config).read()))
-        print(f"random weights for {args.random_config} -> {args.device} ({args.dtype}) ...")
+        raw = preset(args.random_preset) if args.random_preset else json.loads(open(args.random_config).read())
+        cfg: ModelConfig = config_from_dict(raw)
+        print(f"random weights for {args.random_preset or args.random_config} -> {args.device} ({args.dtype}) ...")
         runner = ModelRunner.from_random(cfg, seed=args.seed, **kw)
     engine = Engine(runner, max_running=args.max_running, watermark_blocks=args.watermark_blocks,
                     chunked_budget=args.chunked_budget, default_eos_ids=())
