@@ -9,7 +9,9 @@ has them (``--model-dir --device --num-blocks --page-size --max-running --waterm
 Added: ``--random-config FILE`` (a config.json: random weights are drawn on the device, no
 model folder needed) or ``--random-preset NAME`` (the sizes of a published model, e.g. qwen3-8b), ``--dtype``, ``--chunked-budget``, and ``--prompt-range LO HI`` /
 ``--output-range LO HI`` for requests of mixed lengths (the continuous-batching workload:
-all requests arrive at once, prompts and outputs uniform in the ranges).
+all requests arrive at once, prompts and outputs uniform in the ranges).  The engine warms its
+kernels and decode graphs when it is built (``ModelRunner.warm_up``; ``--no-engine-warm-up`` leaves
+that to the first requests, as the reference does).
 """
 
 from __future__ import annotations
@@ -88,6 +90,7 @@ def main(argv=None) -> int:
     p.add_argument("--output-range", type=int, nargs=2, default=None, metavar=("LO", "HI"))
     p.add_argument("--concurrency", type=int, nargs="+", default=[1, 4, 8])
     p.add_argument("--seed", type=int, default=20261027)
+    p.add_argument("--no-engine-warm-up", action="store_true", help="do not warm kernels and decode graphs at load")
     args = p.parse_args(argv)
     if sum(x is not None for x in (args.model_dir, args.random_config, args.random_preset)) != 1:
         p.error("give exactly one of --model-dir, --random-config and --random-preset")
@@ -103,6 +106,10 @@ def main(argv=None) -> int:
         cfg: ModelConfig = config_from_dict(raw)
         print(f"random weights for {args.random_preset or args.random_config} -> {args.device} ({args.dtype}) ...")
         runner = ModelRunner.from_random(cfg, seed=args.seed, **kw)
+    if not args.no_engine_warm_up:
+        t0 = time.perf_counter()
+        runner.warm_up(decode_rows=tuple(sorted({1, 2, 4, 8} | set(args.concurrency))))
+        print(f"engine warm-up {time.perf_counter() - t0:.2f}s")
     engine = Engine(runner, max_running=args.max_running, watermark_blocks=args.watermark_blocks,
                     chunked_budget=args.chunked_budget, default_eos_ids=())
     vocab = runner.vocab_size

@@ -99,6 +99,35 @@ class ModelRunner:
     def close(self, cache: RequestCache) -> None:
         self.manager.close(cache)
 
+    def warm_up(self, prompt_tokens: tuple[int, ...] = (16, 128, 512, 2048, 8192),
+                decode_rows: tuple[int, ...] = (1, 2, 4, 8)) -> None:
+        """Runs throw-away steps so that what a first request would pay for is paid at load: the
+        library's kernels for prompt portions of several sizes (it loads them when first used) and
+        the captured graphs of small all-decode steps.  Sizes the pools cannot hold are left out;
+        every page and slot is given back."""
+        free = min(self.manager.free_pages()) if self.manager.groups else 0
+        page = self.manager.page_size
+        for T in sorted(set(prompt_tokens)):
+            if T > self.max_step_tokens or -(-T // page) > free or self.manager.slots.num_free < 1:
+                continue
+            rc = self.open(("warm-up", T))
+            try:
+                self.step([StepEntry(rc, [0] * T, [T - 1])])
+            finally:
+                self.close(rc)
+        for R in sorted(set(decode_rows)):
+            if R > self.manager.slots.num_free or R > free:
+                continue
+            rcs = [self.open(("warm-up", R, i)) for i in range(R)]
+            try:
+                self.step([StepEntry(rc, [0], [0]) for rc in rcs])       # the requests' first token
+                for _ in range(3):                                        # seen, captured, replayed
+                    self.step([StepEntry(rc, [0], [0]) for rc in rcs])
+            finally:
+                for rc in rcs:
+                    self.close(rc)
+        torch.cuda.synchronize(self.device)
+
     # ------------------------------------------------------------------ the step
 
     def reserve(self, entries: list[StepEntry]) -> None:

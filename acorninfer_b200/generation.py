@@ -19,11 +19,16 @@ from .sampling.params import SamplingParams
 
 def build_engine(model_dir: str | Path, *, dtype: str = "bfloat16", device: str = "cuda:0", num_blocks: int = 1024,
                  page_size: int = 16, max_running: int = 8, watermark_blocks: int = 8,
-                 chunked_budget: int | None = None) -> Engine:
+                 chunked_budget: int | None = None, warm_up: bool = False) -> Engine:
+    """``warm_up``: run throw-away steps now (``ModelRunner.warm_up``) so that the first requests do not
+    pay for kernels loaded and graphs captured at first use; worth it for an engine that serves."""
     cfg = EngineConfig(model_dir=str(model_dir), device=device, dtype=dtype, num_blocks=num_blocks,
                        page_size=page_size, max_running=max_running, watermark_blocks=watermark_blocks,
                        chunked_budget=chunked_budget)
-    return Engine.from_config(cfg)
+    engine = Engine.from_config(cfg)
+    if warm_up:
+        engine.runner.warm_up()
+    return engine
 
 
 def generate_with_engine(engine: Engine, prompts: list[list[int]], *, max_new_tokens: int = 64,

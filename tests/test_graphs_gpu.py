@@ -52,3 +52,19 @@ def test_bench_module_runs(tmp_path, capsys):
                "--chunked-budget", "16"])
     out = capsys.readouterr().out
     assert rc == 0 and out.count("RESULT C=") == 2 and "tok_s=" in out
+
+
+def test_warm_up_captures_graphs_and_gives_everything_back(tmp_path):
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.engine.runner import ModelRunner
+    from tests.tiny import TINY_D, make_model_dir
+    d = make_model_dir(tmp_path / "m", TINY_D)
+    runner = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=64, page_size=TINY_D["page_size"], max_requests=4)
+    runner.warm_up(prompt_tokens=(16, 100, 10 ** 6), decode_rows=(1, 2, 9))     # sizes beyond the pools are left out
+    runner.manager.assert_balanced()
+    assert min(runner.manager.free_pages()) == 64 and runner.manager.slots.num_free == 4
+    before = runner.graph_replays
+    a = runner.open("a")
+    runner.step([StepEntry(a, [1, 2, 3], [])])
+    runner.step([StepEntry(a, [4], [0])])
+    assert runner.graph_replays == before + 1          # the first decode step of a request replays a warmed graph
