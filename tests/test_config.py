@@ -84,3 +84,16 @@ def test_engine_config_validation():
                 dict(watermark_blocks=1024), dict(chunked_budget=0), dict(dtype="fp8")):
         with pytest.raises(ValueError):
             EngineConfig(**bad)
+
+
+def test_presets_of_the_family_are_valid_configurations():
+    from acorninfer_b200.config.presets import PRESETS, preset
+    from acorninfer_b200.registry import config_from_dict, spec_for
+    for name, raw in PRESETS.items():
+        cfg = config_from_dict(raw)
+        assert cfg.head_dim == 128 and cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        spec_for(cfg)                                    # builds the model description
+    assert preset("Qwen3-8B")["hidden_size"] == 4096
+    import pytest
+    with pytest.raises(ValueError, match="qwen3-8b"):
+        preset("qwen9")
