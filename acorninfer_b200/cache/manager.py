@@ -55,14 +55,17 @@ class RequestCache:
 
 
 class CacheManager:
-    def __init__(self, kv_needs: dict[int, KVNeeds], state_needs: dict[int, StateNeeds], num_pages: int,
+    def __init__(self, kv_needs: dict[int, KVNeeds], state_needs: dict[int, StateNeeds], num_pages,
                  page_size: int, num_slots: int, dtype=None, device=None, allocate: bool = True):
         """``kv_needs`` / ``state_needs`` map schedule-entry index -> what that entry's mixer
-        keeps.  ``num_pages`` is the size of every group's pool."""
+        keeps.  ``num_pages`` is the size of every group's pool, or a function
+        ``KVNeeds -> pages`` that sizes each group's pool by what it keeps (a windowed group
+        needs far fewer pages than one that keeps every key).  ``dtype`` is the element type of
+        groups whose ``KVNeeds.dtype`` names none."""
         if page_size < 1 or page_size & (page_size - 1):
             raise ValueError(f"page_size must be a power of two, got {page_size}")
         self.page_size = page_size
-        self.num_pages = num_pages
+        pages_for = num_pages if callable(num_pages) else (lambda needs: num_pages)
         self.groups: list[CacheGroup] = []
         self.entry_group: dict[int, tuple[int, int]] = {}     # entry -> (group index, layer index in group)
         by_key: dict[tuple, CacheGroup] = {}
@@ -70,7 +73,7 @@ class CacheManager:
             needs = kv_needs[entry]
             g = by_key.get(needs.group_key)
             if g is None:
-                g = CacheGroup(len(self.groups), needs, [], IdPool(num_pages, "page"))
+                g = CacheGroup(len(self.groups), needs, [], IdPool(int(pages_for(needs)), "page"))
                 by_key[needs.group_key] = g
                 self.groups.append(g)
             self.entry_group[entry] = (g.index, len(g.entries))
@@ -79,18 +82,20 @@ class CacheManager:
         self.state_needs = dict(state_needs)
         self.state: dict[int, object] = {}
         self.live: dict[object, RequestCache] = {}
+        self.num_pages = max((g.pool.total for g in self.groups), default=0)
         # One page per group and one slot beyond the pools, never handed out: rows that only pad a
         # step to a captured shape write their keys, values and state there.
-        self.pad_page = num_pages
+        self.pad_pages = [g.pool.total for g in self.groups]
         self.pad_slot = num_slots
         if allocate:
             import torch
             for g in self.groups:
                 n = g.needs
-                g.storage = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
-                                        dtype=dtype, device=device)
+                g.storage = torch.zeros((len(g.entries), 2, g.pool.total + 1, n.num_kv_heads, page_size, n.head_dim),
+                                        dtype=n.dtype or dtype, device=device)
             for entry, sn in self.state_needs.items():
-                self.state[entry] = torch.zeros((num_slots + 1, *sn.shape), dtype=torch.float32, device=device)
+                self.state[entry] = torch.zeros((num_slots + 1, *sn.shape), dtype=sn.dtype or torch.float32,
+                                                device=device)
 
     # ------------------------------------------------------------------ storage views
 
@@ -172,6 +177,17 @@ class CacheManager:
                     f"{g.pool.num_free} free of {g.pool.total}")
         for g, n in zip(self.groups, need):
             rc.tables[g.index].extend(g.pool.allocate(n))
+
+    def trim(self, rc: RequestCache) -> None:
+        """Gives back the pages taken by ``extend`` beyond the committed length: for a step that
+        reserved its pages and then could not be launched."""
+        keep_to = ceil_div(rc.length, self.page_size)
+        for g in self.groups:
+            table = rc.tables[g.index]
+            keep = max(0, keep_to - rc.page_base[g.index])
+            if len(table) > keep:
+                g.pool.free(table[keep:])
+                del table[keep:]
 
     def commit(self, rc: RequestCache, new_length: int) -> None:
         """Records that the step wrote up to ``new_length``; windowed groups give back the pages

@@ -241,12 +241,12 @@ static int launch_decode(const DecodeParams& p, int n, cudaStream_t stream) {
     const size_t kv_bytes = (size_t)2 * DEC_STAGES * DEC_CHUNK * LDS * sizeof(bf16);
     const size_t merge_bytes = (size_t)(128 + 64 * D) * sizeof(float);
     const size_t smem = kv_bytes > merge_bytes ? kv_bytes : merge_bytes;
-    static bool configured = false;
-    if (!configured) {
+    static AcornPerDevice configured;
+    if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured.mark();
     }
     dim3 grid(p.nkv, p.num_splits, n);
     return acorn_launch(attention_decode_kernel<D>, grid, dim3(DEC_THREADS), smem, stream, p);

@@ -275,12 +275,12 @@ extern "C" int acorn_attention_decode_tma_main(const void* q, int64_t q_stride, 
     rc = make_map(&mv, v_pages, num_pages * nkv * P, d, d, 64, box_rows);
     if (rc) return rc;
     const size_t smem = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16;
-    static bool configured = false;
-    if (!configured) {
+    static AcornPerDevice configured;
+    if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured.mark();
     }
     return acorn_launch(attention_decode_tma_kernel, dim3(nkv, num_splits, n), dim3(DT_THREADS), smem, stream, mk, mv, p);
 }

@@ -182,12 +182,12 @@ template <int D>
 static int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
     constexpr int LDS = D + 8;
     const size_t smem = (size_t)2 * 2 * PRE_BN * LDS * sizeof(bf16);
-    static bool configured = false;
-    if (!configured) {
+    static AcornPerDevice configured;
+    if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured.mark();
     }
     dim3 grid(n_tiles, p.nq);
     attention_prefill_kernel<D><<<grid, PRE_THREADS, smem, stream>>>(p);

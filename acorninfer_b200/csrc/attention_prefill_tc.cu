@@ -398,12 +398,12 @@ extern "C" int acorn_attention_prefill_tc(const void* q, int64_t q_stride, int t
     rc = make_map(&mv, v_pages, num_pages * nkv * P, d, d, 64, box_rows);
     if (rc) return rc;
     const size_t smem = ATC_SMEM_TILES + ATC_NUM_BARS * 8 + 16;
-    static bool configured = false;
-    if (!configured) {
+    static AcornPerDevice configured;
+    if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured.mark();
     }
     return acorn_launch(attention_prefill_tc_kernel, dim3((unsigned)ctas), dim3(ATC_THREADS), smem, stream, mq, mk, mv, p);
 }

@@ -100,6 +100,24 @@ template <> struct Vec4<bf16> {
 
 static inline int acorn_launch_status() { return (int)cudaGetLastError(); }
 
+// Function attributes (the dynamic shared memory limit) are set per device: a launcher keeps one of
+// these as a static and configures its kernel the first time it runs on each device.
+struct AcornPerDevice {
+    bool done[64] = {};
+    static int current() {
+        int dev = 0;
+        return cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 ? dev : -1;
+    }
+    bool seen() const {
+        const int dev = current();
+        return dev >= 0 && done[dev];
+    }
+    void mark() {
+        const int dev = current();
+        if (dev >= 0) done[dev] = true;
+    }
+};
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // Every kernel of this library is launched with programmatic stream serialization: it may be
 // scheduled while the kernel before it in the stream is still running, and must call

@@ -383,12 +383,12 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     const size_t recv = MB <= 64 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
     const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 +
                         (TC_RED_FLOATS(MB) + MB) * sizeof(float) + recv + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static AcornPerDevice configured;
+    if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MB, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured.mark();
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.N + TC_BM - 1) / TC_BM, (p.M + MB - 1) / MB, splits);

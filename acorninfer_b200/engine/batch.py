@@ -11,6 +11,13 @@ Arrays (int32), T tokens, R rows, W wanted logits, per cache group g:
   token_row[T], row_start[R+1] (offsets into the token arrays), row_pos[R] (tokens of
   the request in the cache before this step), row_slot[R], logit_tokens[W],
   g.kv_len[R] (row_pos + the row's tokens), g.page_base[R], g.block_table[R, stride].
+
+This layer knows nothing of any kernel's tiling.  A part whose kernels need further per-step
+arrays (query tiles of an attention kernel, a scan's chunk table, expert offsets) declares them
+through ``Part.step_arrays()``: a name and a builder ``StepPlan -> int32 ndarray``.  The builders
+of all parts of a model are handed to ``plan_step``; their arrays travel in the same single
+upload and reach the part as ``StepInputs.extra[name]`` (device) and ``StepPlan.extra[name]``
+(host).  A builder must be a function of the plan alone.
 """
 
 from __future__ import annotations
@@ -61,22 +68,13 @@ class StepPlan:
     row_lens: list[int]
     max_q_len: int
     all_decode: bool            # every row is a single token
-    q_tiles: np.ndarray = None  # [n_tiles, 2]: (row, first token within the row) of each 64-token query tile
-                                # of the rows that bring more than one token
-    single_tokens: np.ndarray = None   # flat indices of the tokens of single-token rows (decoded tokens)
-    q_tiles_large: np.ndarray = None   # the same rows cut for kernels with TILE_LARGE queries a tile:
-    q_tiles_small: np.ndarray = None   # rows of at least LARGE_MIN tokens in large tiles, shorter ones in Q_TILE tiles
     patch_dst: np.ndarray = None       # flat token indices whose ids come from the device ...
     patch_src: np.ndarray = None       # ... and where among the previous step's sampled tokens they are
+    extra: dict = field(default_factory=dict)    # arrays the model's parts declared, by name (any shape, int32)
 
     @property
     def num_logits(self) -> int:
         return int(self.logit_tokens.size)
-
-
-Q_TILE = 64     # query tokens per tile of the prefill attention kernel
-TILE_LARGE = 128   # query tokens per tile of the tcgen05 prefill attention kernel
-LARGE_MIN = 32     # rows shorter than this stay with the small-tile kernel
 
 
 def _table_stride(pages: int) -> int:
@@ -114,8 +112,18 @@ def validate_entries(entries: list[StepEntry], vocab_size: int, max_tokens: int 
         raise BatchError(f"step has {total} tokens, the workspace holds {max_tokens}")
 
 
-def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
-    """Lays out a validated step whose pages are already reserved (``manager.extend`` done)."""
+def build_extra(plan: StepPlan, builders: dict | None) -> dict:
+    """The arrays the parts declared, built for ``plan``."""
+    out = {}
+    for name, build in (builders or {}).items():
+        arr = np.ascontiguousarray(build(plan), dtype=np.int32)
+        out[name] = arr
+    return out
+
+
+def plan_step(entries: list[StepEntry], manager: CacheManager, builders: dict | None = None) -> StepPlan:
+    """Lays out a validated step whose pages are already reserved (``manager.extend`` done).
+    ``builders``: name -> function of the plan, for the arrays the model's parts declared."""
     R = len(entries)
     lens = [len(e.tokens) for e in entries]
     T = sum(lens)
@@ -154,19 +162,12 @@ def plan_step(entries: list[StepEntry], manager: CacheManager) -> StepPlan:
             kv_len[r] = new_len
             base[r] = e.cache.page_base[g.index]
         groups.append(GroupPlan(kv_len, base, bt, int(kv_len.max()) if R else 0))
-    # Rows of one token go to the decode attention kernel, longer rows to the prefill kernel in
-    # tiles of Q_TILE queries.  When a kernel does not take the model's head size, the caller
-    # falls back to the plain kernel for all tokens.
-    tiles = [(r, q0) for r, n in enumerate(lens) if n > 1 for q0 in range(0, n, Q_TILE)]
-    singles = [int(row_start[r]) for r, n in enumerate(lens) if n == 1]
-    large = [(r, q0) for r, n in enumerate(lens) if n >= LARGE_MIN for q0 in range(0, n, TILE_LARGE)]
-    small = [(r, q0) for r, n in enumerate(lens) if 1 < n < LARGE_MIN for q0 in range(0, n, Q_TILE)]
-    as_tiles = lambda t: np.asarray(t, np.int32).reshape(-1, 2)
     patch = [(int(row_start[r]), e.from_device) for r, e in enumerate(entries) if e.from_device is not None]
-    return StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
+    plan = StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,
                     np.asarray(logit_tokens, np.int32), groups, lens, max(lens), all(n == 1 for n in lens),
-                    as_tiles(tiles), np.asarray(singles, np.int32), as_tiles(large), as_tiles(small),
                     np.asarray([p[0] for p in patch], np.int32), np.asarray([p[1] for p in patch], np.int32))
+    plan.extra = build_extra(plan, builders)
+    return plan
 
 
 # Row counts that all-decode steps are padded to, so that few shapes are captured as CUDA graphs.
@@ -180,10 +181,11 @@ def decode_bucket(n: int) -> int:
     return -(-n // 32) * 32
 
 
-def pad_decode_plan(plan: StepPlan, pad_page: int, pad_slot: int) -> StepPlan:
+def pad_decode_plan(plan: StepPlan, pad_pages: list[int], pad_slot: int, builders: dict | None = None) -> StepPlan:
     """An all-decode plan padded to its bucket: the added rows feed token 0 at position 0 of a
-    request that exists only as the manager's padding page and slot; the added wanted places point
-    at them.  Callers use the first ``plan.num_rows`` / ``plan.num_logits`` results only."""
+    request that exists only as the manager's padding pages (one per cache group) and slot; the added wanted places point
+    at them.  Callers use the first ``plan.num_rows`` / ``plan.num_logits`` results only.  The parts'
+    arrays are built again for the padded plan, so their sizes follow the bucket."""
     R, W = plan.num_rows, plan.num_logits
     Rb, Wb = decode_bucket(R), decode_bucket(W) if W else 0
     if Rb == R and Wb == W:
@@ -192,18 +194,19 @@ def pad_decode_plan(plan: StepPlan, pad_page: int, pad_slot: int) -> StepPlan:
     i32 = np.int32
     cat = lambda a, fill, n: np.concatenate([a, np.full(n, fill, i32)])
     groups = []
-    for g in plan.groups:
+    for g, pad_page in zip(plan.groups, pad_pages):
         bt = np.zeros((Rb, g.block_table.shape[1]), i32)
         bt[:R] = g.block_table
         bt[R:, 0] = pad_page
         groups.append(GroupPlan(cat(g.kv_len, 1, extra), cat(g.page_base, 0, extra), bt, g.max_kv_len))
     pad_target = R if extra else 0                     # a padding row if there is one, else any row
-    return StepPlan(
+    padded = StepPlan(
         Rb, Rb, cat(plan.token_ids, 0, extra), cat(plan.positions, 0, extra),
         np.arange(Rb, dtype=i32), np.arange(Rb + 1, dtype=i32), cat(plan.row_pos, 0, extra),
         cat(plan.row_slot, pad_slot, extra), cat(plan.logit_tokens, pad_target, Wb - W), groups,
-        plan.row_lens + [1] * extra, 1, True, plan.q_tiles, np.arange(Rb, dtype=i32), plan.q_tiles_large,
-        plan.q_tiles_small, plan.patch_dst, plan.patch_src)
+        plan.row_lens + [1] * extra, 1, True, plan.patch_dst, plan.patch_src)
+    padded.extra = build_extra(padded, builders)
+    return padded
 
 
 # --------------------------------------------------------------------------- device side
@@ -232,12 +235,9 @@ class StepInputs:
     logit_tokens: object
     groups: list[GroupInputs]
     plan: StepPlan
-    q_tiles: object = None
-    single_tokens: object = None
-    q_tiles_large: object = None
-    q_tiles_small: object = None
     patch_dst: object = None
     patch_src: object = None
+    extra: dict = field(default_factory=dict)    # device views of the arrays the parts declared, by name
 
     @property
     def num_logits(self) -> int:
@@ -247,9 +247,12 @@ class StepInputs:
 class StepWorkspace:
     """Pinned staging blocks and a device block that a step's arrays are packed into.
 
-    The layout is a function of (T, R, W, strides) only, so two steps of the same shape
-    put every array at the same device address: a captured CUDA graph of one can be
-    replayed for the other after ``upload``.
+    The address of every array a model reads is a function of ``shape_key(plan)``: (T, R, W,
+    the groups' table strides, the sizes of the parts' arrays).  Two steps of the same key put
+    those arrays at the same device addresses, so a captured CUDA graph of one can be replayed
+    for the other after ``upload``.  ``patch_dst`` / ``patch_src`` (read by the patch kernel,
+    which runs outside any captured graph) vary in size between steps of one key and therefore
+    lie behind everything else.
     """
 
     def __init__(self, device, capacity_ints: int = 1 << 20, num_staging: int = 3):
@@ -281,17 +284,21 @@ class StepWorkspace:
         put("row_pos", R)
         put("row_slot", R)
         put("logit_tokens", plan.num_logits)
-        put("q_tiles", plan.q_tiles.size)
-        put("single_tokens", plan.single_tokens.size)
-        put("q_tiles_large", plan.q_tiles_large.size)
-        put("q_tiles_small", plan.q_tiles_small.size)
-        put("patch_dst", plan.patch_dst.size)
-        put("patch_src", plan.patch_src.size)
         for i, g in enumerate(plan.groups):
             put(f"g{i}.kv_len", R)
             put(f"g{i}.page_base", R)
             put(f"g{i}.block_table", g.block_table.size)
+        for name in sorted(plan.extra):
+            put("x." + name, plan.extra[name].size)
+        put("patch_dst", plan.patch_dst.size)       # last: their sizes are not part of the shape key
+        put("patch_src", plan.patch_src.size)
         return out, off
+
+    @staticmethod
+    def shape_key(plan: StepPlan) -> tuple:
+        """What fixes the address of every array but the patch lists (see the class docstring)."""
+        return (plan.num_tokens, plan.num_rows, plan.num_logits, tuple(g.block_table.shape[1] for g in plan.groups),
+                tuple((name, plan.extra[name].shape) for name in sorted(plan.extra)))
 
     def upload(self, plan: StepPlan) -> StepInputs:
         torch = self.torch
@@ -306,10 +313,10 @@ class StepWorkspace:
         arrays = {
             "token_ids": plan.token_ids, "positions": plan.positions, "token_row": plan.token_row,
             "row_start": plan.row_start, "row_pos": plan.row_pos, "row_slot": plan.row_slot,
-            "logit_tokens": plan.logit_tokens, "q_tiles": plan.q_tiles.reshape(-1),
-            "single_tokens": plan.single_tokens, "q_tiles_large": plan.q_tiles_large.reshape(-1),
-            "q_tiles_small": plan.q_tiles_small.reshape(-1), "patch_dst": plan.patch_dst, "patch_src": plan.patch_src,
+            "logit_tokens": plan.logit_tokens, "patch_dst": plan.patch_dst, "patch_src": plan.patch_src,
         }
+        for name, arr in plan.extra.items():
+            arrays["x." + name] = arr.reshape(-1)
         for gi, g in enumerate(plan.groups):
             arrays[f"g{gi}.kv_len"] = g.kv_len
             arrays[f"g{gi}.page_base"] = g.page_base
@@ -332,5 +339,5 @@ class StepWorkspace:
             groups.append(GroupInputs(view(f"g{gi}.kv_len"), view(f"g{gi}.page_base"), bt, g.max_kv_len))
         return StepInputs(plan.num_tokens, plan.num_rows, view("token_ids"), view("positions"), view("token_row"),
                           view("row_start"), view("row_pos"), view("row_slot"), view("logit_tokens"), groups, plan,
-                          view("q_tiles").view(-1, 2), view("single_tokens"), view("q_tiles_large").view(-1, 2),
-                          view("q_tiles_small").view(-1, 2), view("patch_dst"), view("patch_src"))
+                          view("patch_dst"), view("patch_src"),
+                          {name: view("x." + name).view(arr.shape) for name, arr in plan.extra.items()})

@@ -3,7 +3,8 @@
 ``ModelRunner`` owns the model, the cache manager and the step workspace.  ``step``
   1. validates the batch on the host (a bad batch raises; nothing ran, nothing is held),
   2. reserves the pages the step writes (all requests or none: ``PoolExhausted``),
-  3. lays the batch out and uploads it in one transfer,
+  3. lays the batch out and uploads it in one transfer (a step whose arrays do not fit the
+     workspace raises ``BatchError`` here; the pages of 2 are given back first),
   4. runs the model over exactly the tokens given, reading earlier tokens from the cache,
   5. commits the new lengths (windowed groups give pages back),
 and returns float32 logits ``[wanted, vocab]`` in the order of the entries and their
@@ -38,7 +39,8 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 class ModelRunner:
     def __init__(self, config: ModelConfig, tensors: dict[str, torch.Tensor] | None, *, dtype: str = "bfloat16",
                  device: str = "cuda:0", num_blocks: int = 1024, page_size: int = 16, max_requests: int = 64,
-                 max_step_tokens: int = 8192, decoder: Decoder | None = None, decode_graph: bool = True):
+                 max_step_tokens: int = 8192, decoder: Decoder | None = None, decode_graph: bool = True,
+                 workspace_ints: int = 1 << 20):
         self.config = config
         self.dtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
         self.device = torch.device(device)
@@ -53,7 +55,8 @@ class ModelRunner:
                                     dtype=self.dtype, device=self.device)
         self.caches = self.decoder.entry_caches(self.manager)
         self.max_step_tokens = max_step_tokens
-        self.workspace = StepWorkspace(self.device)
+        self.step_arrays = self.decoder.step_arrays()     # per-step arrays the parts' kernels read
+        self.workspace = StepWorkspace(self.device, workspace_ints)
         self.vocab_size = self.spec.vocab_size
         # CUDA graphs of all-decode steps, keyed by the sizes that fix every launch of the step
         self.decode_graph = decode_graph and self.decoder.graph_safe
@@ -151,13 +154,18 @@ class ModelRunner:
         if device_tokens is None and any(e.from_device is not None for e in entries):
             raise BatchError("entries take ids from the device but no device_tokens were given")
         self.reserve(entries)
-        plan = plan_step(entries, self.manager)
-        self.last_plan = plan
-        graph = self.decode_graph and plan.all_decode
-        if graph:
-            # padded to a bucket of row counts, so that a few captured graphs serve every batch size
-            plan = pad_decode_plan(plan, self.manager.pad_page, self.manager.pad_slot)
-        inputs = self.workspace.upload(plan)
+        try:
+            plan = plan_step(entries, self.manager, self.step_arrays)
+            self.last_plan = plan
+            graph = self.decode_graph and plan.all_decode
+            if graph:
+                # padded to a bucket of row counts, so that a few captured graphs serve every batch size
+                plan = pad_decode_plan(plan, self.manager.pad_pages, self.manager.pad_slot, self.step_arrays)
+            inputs = self.workspace.upload(plan)
+        except Exception:
+            for e in entries:           # nothing was launched: the step holds nothing
+                self.manager.trim(e.cache)
+            raise
         if plan.patch_dst.size:
             ops.patch_tokens(inputs.token_ids, inputs.patch_dst, inputs.patch_src, device_tokens)
         if graph:
@@ -175,10 +183,10 @@ class ModelRunner:
     def _decode_step(self, plan, inputs):
         """An all-decode step: replayed from a CUDA graph once its shape has been seen twice.
 
-        The step arrays were just uploaded to the addresses the graph reads (the workspace's
-        layout is a function of the key), so a replay is this step.  The returned logits are
-        the graph's output buffer: valid until the next step."""
-        key = (plan.num_rows, plan.num_logits, tuple(g.block_table.shape[1] for g in plan.groups))
+        The step arrays were just uploaded to the addresses the graph reads (the address of every
+        array the model reads is a function of the key), so a replay is this step.  The returned
+        logits are the graph's output buffer: valid until the next step."""
+        key = self.workspace.shape_key(plan)
         entry = self._graphs.get(key)
         if entry is not None:
             graph, logits, launches = entry

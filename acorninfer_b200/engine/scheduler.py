@@ -10,10 +10,15 @@ its pages are given back, it returns to the front of the waiting queue and is la
 recomputed from its prompt plus what it had generated.  A request preempted in a step
 is not admitted again in the same step.
 
-Differences from the reference, both deliberate: the budget counts every token of the
+Differences from the reference, all deliberate: the budget counts every token of the
 step (decoded tokens first, prompt portions fill the rest; the reference's budget covers
-prompt tokens only, ``:72-76``), and page arithmetic is per cache group, since groups
-(all keys, a window of them) have pools of their own.
+prompt tokens only, ``:72-76``); a request that is recomputed after a preemption is cut
+into portions under the budget like any prompt (the reference exempts it from the budget,
+``:140-143``, and recomputes it in one piece); page arithmetic is per cache group, since
+groups (all keys, a window of them) have pools of their own; and when the engine runs a
+step ahead of the host, a running request whose last allowed token is already sampled is
+the first to give its pages up (it runs no more, so nothing is recomputed) and is not
+queued again.
 
 The scheduler decides; it touches no device.  It calls ``manager.close`` when it preempts
 and ``manager.open`` when it admits, so page counts it reads are always current.
@@ -99,10 +104,21 @@ class Scheduler:
                 need[gi] += n
         return portions, need, budget
 
+    def _pick_victim(self) -> Request:
+        """A request that will not run again (its last allowed token is sampled; the host has not
+        read it yet) if there is one: its pages are of no further use.  Else the oldest."""
+        for r in self.running:
+            if r.exhausted:
+                return r
+        return self.running[0]
+
     def _preempt(self, victim: Request) -> None:
+        self.running.remove(victim)
         self.manager.close(victim.cache)
         victim.cache = None
         victim.cursor = 0
+        if victim.exhausted:
+            return              # it only waits for its last token to be read; nothing to recompute
         victim.status = RequestStatus.WAITING
         victim.preemptions += 1
         self.waiting.appendleft(victim)
@@ -111,13 +127,17 @@ class Scheduler:
 
     def schedule(self) -> StepDecision:
         decision = StepDecision()
+        # A preempted request may have ended on the token that was still on its way to the host
+        # when it was queued again: it has nothing left to run.
+        if any(r.is_finished for r in self.waiting):
+            self.waiting = deque(r for r in self.waiting if not r.is_finished)
         # 1. what the running requests need this step; preempt the oldest until it fits
         while True:
             portions, need, budget_left = self._plan_running(self._budget())
             free = self.manager.free_pages()
             if all(n <= f for n, f in zip(need, free)) or not self.running:
                 break
-            victim = self.running.pop(0)
+            victim = self._pick_victim()
             self._preempt(victim)
             decision.preempted.append(victim)
         reserve = need

@@ -8,13 +8,52 @@ sizes and group sizes the fast kernels do not take.
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from . import ops
 
-NUM_SMS = 148
-_TARGET_CTAS = NUM_SMS * 2
+B200_SMS = 148          # what planning functions assume when no device is given (CPU-side tests)
 _CHUNK = 64
+
+Q_TILE = 64             # query tokens per tile of the mma.sync prefill kernel
+TILE_LARGE = 128        # query tokens per tile of the tcgen05 prefill kernel
+LARGE_MIN = 32          # rows shorter than this stay with the small-tile kernel
+
+
+def _tiles(plan, lo: int, hi: int | None, tile: int) -> np.ndarray:
+    """(row, first token within the row) of every ``tile``-token query tile of the rows that bring
+    lo <= n (< hi) tokens."""
+    t = [(r, q0) for r, n in enumerate(plan.row_lens) if n >= lo and (hi is None or n < hi)
+         for q0 in range(0, n, tile)]
+    return np.asarray(t, np.int32).reshape(-1, 2)
+
+
+def _single_tokens(plan) -> np.ndarray:
+    return np.asarray([int(plan.row_start[r]) for r, n in enumerate(plan.row_lens) if n == 1], np.int32)
+
+
+def _large_tiles(plan) -> np.ndarray:
+    """Tiles of the tcgen05 kernel, longest first: a tile's work grows with the keys before its
+    last query (the row's cached length plus the tile's end), and CTAs are handed out in list
+    order, so the long ones start first and the short ones fill the tail of the last wave."""
+    t = _tiles(plan, LARGE_MIN, None, TILE_LARGE)
+    if t.shape[0] > 1:
+        keys = plan.row_pos[t[:, 0]] + np.minimum(t[:, 1] + TILE_LARGE, np.asarray(plan.row_lens, np.int32)[t[:, 0]])
+        t = t[np.argsort(-keys, kind="stable")]
+    return np.ascontiguousarray(t)
+
+
+# The per-step arrays the attention kernels read (``Part.step_arrays``): rows of one token go to the
+# decode kernel by token list, longer rows to a prefill kernel in query tiles.
+STEP_ARRAYS = {
+    "attention.single_tokens": _single_tokens,
+    "attention.q_tiles": lambda plan: _tiles(plan, 2, None, Q_TILE),
+    "attention.q_tiles_large": _large_tiles,
+    "attention.q_tiles_small": lambda plan: _tiles(plan, 2, LARGE_MIN, Q_TILE),
+}
+
+sm_count = ops.device_sms
 
 
 # What the split choice assumes of the decode kernel on this GPU (measured: 10 to 128 rows of 8 kv
@@ -24,16 +63,17 @@ _CHUNK = 64
 _CTA_GBS, _HBM_GBS, _WAVE_US, _MERGE_US = 35.0, 6500.0, 2.0, 3.0
 
 
-def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int = 128) -> int:
+def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, num_sms: int = B200_SMS) -> int:
     """Splits of the key range.  ``key_bound`` bounds the keys any row reads; it changes only with
     the table stride, so a captured step keeps its grid.
 
-    Two CTAs of the decode kernel fit on an SM: 296 run at a time, in waves.  A CTA is bound by
+    Two CTAs of the decode kernel fit on an SM: ``2 * num_sms`` (296 on a B200) run at a time, in waves.  A CTA is bound by
     its own streaming rate, a full wave by the memory.  So few (row, kv head) pairs want many
     splits (more CTAs in flight); a count just above a multiple of 296 wants splits too (a last
     wave of few long CTAs takes as long as one CTA takes alone: 40 rows of 8 kv heads, unsplit,
     take 149 us against 123 us in three splits); a count that fills its last wave well wants
     none.  The splits with the least estimated time are taken."""
+    _TARGET_CTAS = 2 * num_sms
     pairs = max(1, rows * num_kv_heads)
     most = max(1, min(-(-key_bound // _CHUNK), 32))
     pair_kb = key_bound * head_dim * 4 / 1e3                         # K and V of one pair, bfloat16, in KB
@@ -61,11 +101,12 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             bound = group.block_table.shape[1] * P
             if window:
                 bound = min(bound, window)
-            splits = decode_splits(inputs.num_rows, nkv, bound)
+            splits = decode_splits(inputs.num_rows, nkv, bound, d, sm_count(qkv.device))
             return ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                         group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
                                         nq, nkv, d, scale, window, splits)
-        n_single = int(inputs.plan.single_tokens.size)
+        x, hx = inputs.extra, inputs.plan.extra
+        n_single = int(hx["attention.single_tokens"].size)
         if ops.attention_prefill_supported(nq, nkv, d) and (n_single == 0 or (
                 ops.attention_decode_supported(nq, nkv, d) and n_single <= 65535)):
             # a mixed step: prompt portions through the prefill kernel, decoded tokens through the
@@ -73,17 +114,17 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             out = torch.empty((inputs.num_tokens, nq * d), dtype=qkv.dtype, device=qkv.device)
             if ops.attention_prefill_tc_supported(nq, nkv, d, P) and qkv.stride(0) % 8 == 0:
                 # long rows on the tcgen05 kernel (tiles of 128 queries), short ones on the mma.sync kernel
-                if inputs.q_tiles_large.shape[0]:
+                if hx["attention.q_tiles_large"].shape[0]:
                     ops.attention_prefill_tc(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
-                                             group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles_large,
+                                             group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_large"],
                                              inputs.num_tokens, nq, nkv, d, scale, window, out=out)
-                if inputs.q_tiles_small.shape[0]:
+                if hx["attention.q_tiles_small"].shape[0]:
                     ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
-                                          group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles_small,
+                                          group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles_small"],
                                           inputs.num_tokens, nq, nkv, d, scale, window, out=out)
-            elif inputs.q_tiles.shape[0]:
+            elif hx["attention.q_tiles"].shape[0]:
                 ops.attention_prefill(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
-                                      group.page_base, inputs.row_start, inputs.row_pos, inputs.q_tiles,
+                                      group.page_base, inputs.row_start, inputs.row_pos, x["attention.q_tiles"],
                                       inputs.num_tokens, nq, nkv, d, scale, window, out=out)
             if n_single:
                 bound = group.block_table.shape[1] * P
@@ -91,8 +132,9 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
                     bound = min(bound, window)
                 ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                      group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
-                                     nq, nkv, d, scale, window, decode_splits(n_single, nkv, bound),
-                                     token_list=inputs.single_tokens, out=out)
+                                     nq, nkv, d, scale, window,
+                                     decode_splits(n_single, nkv, bound, d, sm_count(qkv.device)),
+                                     token_list=x["attention.single_tokens"], out=out)
             return out
     return ops.attention_plain(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,

@@ -76,7 +76,7 @@ def bench_attn_decode(a) -> None:
     rows = torch.arange(B, dtype=torch.int32, device=DEV)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
     qkv = torch.randn(B, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
-    splits = a.splits or decode_splits(B, nkv, ctx)
+    splits = a.splits or decode_splits(B, nkv, ctx, d)
     us = _time([lambda: ops.attention_decode(qkv, qkv.stride(0), k_pages, v_pages, table, base, rows, pos, B, nq, nkv,
                                              d, d ** -0.5, None, splits, use_tma=a.kernel != "mma")],
                a.reps, a.graph)

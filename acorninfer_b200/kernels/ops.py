@@ -124,6 +124,7 @@ class _Sigs:
     acorn_sample = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_void_p, c_void_p]
     acorn_uniform = [ctypes.c_uint64, ctypes.c_uint64]
+    acorn_random_fill = [c_void_p, c_int64, ctypes.c_uint64, ctypes.c_uint64, c_float, c_float, c_int, c_void_p]
     acorn_error_word_alloc = [c_void_p, c_void_p]
     acorn_error_word_selftest = [c_int, c_void_p]
     acorn_gemm_tc_set_error_word = [c_void_p]
@@ -489,12 +490,24 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and bool(lib().acorn_gemm_tc_supported(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))))
 
 
-def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int]:
+_SMS: dict = {}
+
+
+def device_sms(device) -> int:
+    """Multiprocessors of ``device`` (asked of the driver once)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _SMS:
+        _SMS[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _SMS[key]
+
+
+def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148) -> tuple[int, int]:
     """(splits of the K range, CTAs to an SM) for a product on the tcgen05 kernel.
 
     Splits: a cluster of that many CTAs per output tile, a power of two, at most 8, chosen so that a
     matrix with few 128-row tiles still puts one to two CTAs on every SM.  CTAs to an SM: two, with
-    a deep ring, or three with a short one (up to 32 rows).  An SM takes in about 66 GB/s, so the SM
+    a deep ring, or three with a short one (up to 32 rows).  ``num_sms`` defaults to a B200's 148;
+    launches pass the device's own count.  An SM takes in about 66 GB/s, so the SM
     with the most tiles sets the time: 192 tiles on 148 SMs leave 44 SMs with two tiles (2.0 tiles'
     worth), while 384 half tiles, three to an SM, leave none with more than three halves (1.5).  The
     second form is taken for unsplit matrices with 1 to 1.5 tiles to an SM; where K is split
@@ -503,9 +516,9 @@ def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int]:
     tiles = -(-N // 128) * -(-M // rows)
     kblocks = -(-K // 64)
     splits = 1
-    while splits < 8 and tiles * splits * 2 <= 2 * 148 and kblocks // (splits * 2) >= 4:
+    while splits < 8 and tiles * splits * 2 <= 2 * num_sms and kblocks // (splits * 2) >= 4:
         splits *= 2
-    if rows <= 32 and splits == 1 and kblocks >= 8 and 148 < tiles and tiles * 2 <= 3 * 148:
+    if rows <= 32 and splits == 1 and kblocks >= 8 and num_sms < tiles and tiles * 2 <= 3 * num_sms:
         return 2, 3                     # more tiles than SMs, fewer than 1.5 to an SM (measured: 36.0 -> 33.3 us)
     return splits, 2
 
@@ -592,7 +605,7 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=xt.device)
     _check(out, "out", torch.bfloat16, 2)
-    splits, per_sm = gemm_tc_plan(M, N, K)
+    splits, per_sm = gemm_tc_plan(M, N, K, device_sms(xt.device))
     _ok(lib().acorn_gemm_tc_qkv_rope(
         xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, K, splits, per_sm,
         rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
@@ -629,7 +642,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
     if (rows is not None or epilogue is not None or swiglu) and M > 64:
         raise KernelError(f"gemm_tc: fused norm / SwiGLU epilogues take at most 64 rows, got {M}")
     if splits is None:
-        splits, per_sm = gemm_tc_plan(M, N, K)
+        splits, per_sm = gemm_tc_plan(M, N, K, device_sms(xt.device))
     mode, resid, ldr, norm_w, ss_out = 0, None, 0, None, None
     out_cols = N
     if epilogue is not None:
@@ -731,6 +744,15 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                            top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(), tokens.data_ptr(),
                            _ptr(logprobs), _stream()), "sample")
     return tokens, logprobs
+
+
+def random_fill(out: torch.Tensor, key: int, first: int, scale: float, offset: float, kind: int) -> torch.Tensor:
+    """Fills ``out`` (flat, contiguous) with elements ``first ..`` of the counter-based random tensor
+    ``key``: ``offset + lane_sum * scale`` (kind 0 float32, 1 bfloat16) or 15-bit integers (kind 2)."""
+    _check(out, "out", {0: torch.float32, 1: torch.bfloat16, 2: torch.int32}[kind])
+    _ok(lib().acorn_random_fill(out.data_ptr(), out.numel(), ctypes.c_uint64(key), ctypes.c_uint64(first),
+                                float(scale), float(offset), kind, _stream()), "random_fill")
+    return out
 
 
 def uniform(seed: int, counter: int) -> float:

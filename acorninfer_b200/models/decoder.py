@@ -2,7 +2,8 @@
 
 ``forward`` is the whole model for one step: token table -> float32 residual stream ->
 the scheduled layer runs -> final norm on the rows whose logits are wanted -> output
-matrix -> float32 logits.  Reference for the order of operations:
+matrix -> float32 logits, with the spec's stages (if it names any) after the token table and
+around the output matrix.  Reference for the order of operations:
 ``Qwen3ForCausalLM.forward`` in ``acorninfer/models/qwen3.py:491-518``.  The layer loop is a
 loop over data: ``spec.schedule`` may name a layer twice, and a run may read the cache
 of an earlier run instead of keeping its own.
@@ -16,7 +17,7 @@ import torch
 
 from .. import parts as _parts  # noqa: F401  (registers the built-in part kinds)
 from ..kernels import ops
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, BuildContext, KVNeeds,
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, STAGES, BuildContext, KVNeeds,
                           ModelSpec, StateNeeds, TensorSpec, build_part)
 
 
@@ -57,6 +58,10 @@ class Decoder:
             self._named_parts.append((ls.block.prefix, block))
         self.final_norm = build_part(NORMS, spec.final_norm, self.ctx)
         self._named_parts.append((spec.final_norm.prefix, self.final_norm))
+        self.stages = {}
+        for where in ("after_embedding", "before_head", "after_head"):
+            self.stages[where] = [build_part(STAGES, ps, self.ctx) for ps in getattr(spec, where)]
+            self._named_parts.extend((ps.prefix, st) for ps, st in zip(getattr(spec, where), self.stages[where]))
         for i, e in enumerate(spec.schedule):
             if not (0 <= e.layer < len(spec.layers)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}; the model has {len(spec.layers)}")
@@ -123,6 +128,14 @@ class Decoder:
             out.append(EntryCache(i, group, k, v, e.reads_cache_of is None, manager.state.get(i)))
         return out
 
+    def step_arrays(self) -> dict:
+        """The per-step arrays all parts declare (``Part.step_arrays``), by name."""
+        out: dict = {}
+        for _, part in self._named_parts:
+            for name, build in part.step_arrays().items():
+                out.setdefault(name, build)
+        return out
+
     @property
     def graph_safe(self) -> bool:
         """Every part allows a step to be captured and replayed (see ``Part.graph_safe``)."""
@@ -133,6 +146,8 @@ class Decoder:
     def forward(self, inputs, caches: list[EntryCache]) -> torch.Tensor | None:
         """Runs the step's tokens; returns float32 logits [wanted, vocab] (None if none wanted)."""
         resid32 = ops.embed(inputs.token_ids, self.embedding)
+        for stage in self.stages["after_embedding"]:
+            resid32 = stage.forward(resid32, inputs)
         delta = None
         sched = self.spec.schedule
         for i, e in enumerate(sched):
@@ -143,7 +158,12 @@ class Decoder:
         if inputs.num_logits == 0:
             return None
         h = self.final_norm.add_forward(resid32, delta, rows=inputs.logit_tokens)
-        return ops.linear(h, self.head, out_dtype=torch.float32)
+        for stage in self.stages["before_head"]:
+            h = stage.forward(h, inputs)
+        logits = ops.linear(h, self.head, out_dtype=torch.float32)
+        for stage in self.stages["after_head"]:
+            logits = stage.forward(logits, inputs)
+        return logits
 
 
 def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:

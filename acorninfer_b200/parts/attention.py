@@ -70,6 +70,9 @@ class Attention(Mixer):
     def cache_needs(self):
         return CacheNeeds(kv=KVNeeds(self.nkv, self.d, self.window))
 
+    def step_arrays(self):
+        return attn_kernels.STEP_ARRAYS
+
     def fusable(self, num_rows):
         return (ops.fused_rows_ok(num_rows, self.ctx.dtype) and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and (self.nq * self.d) % 8 == 0)

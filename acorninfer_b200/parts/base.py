@@ -14,6 +14,7 @@ Interfaces
 ``Mixer``             ``cache_needs()``; ``forward(x, inputs, cache) -> delta``
 ``FeedForward``       ``forward(x, inputs) -> delta``
 ``Block``             ``forward(resid32, delta, inputs, cache) -> (resid32, delta)``
+``Stage``             ``forward(x, inputs) -> x`` outside the layers (after the token table, around the head)
 
 All activations are ``[tokens, width]`` over the flat token dimension of one step.
 The residual stream is kept in float32 (``resid32``); what a part adds to it
@@ -83,6 +84,11 @@ class ModelSpec:
     final_norm: PartSpec
     head: str | None                    # tensor name of the output matrix; None: tied to embedding
     positions: dict[str, PartSpec] = field(default_factory=dict)   # shared position encodings by name
+    # Stages outside the layers (kinds of the STAGES registry), applied in order; empty for a model
+    # that goes from the token table straight into its layers and from the output matrix to logits.
+    after_embedding: tuple[PartSpec, ...] = ()    # on the float32 residual stream [tokens, hidden]
+    before_head: tuple[PartSpec, ...] = ()        # on the normed rows whose logits are wanted [wanted, hidden]
+    after_head: tuple[PartSpec, ...] = ()         # on the float32 logits [wanted, vocab]
 
 
 @dataclass
@@ -99,22 +105,26 @@ class BuildContext:
 @dataclass(frozen=True)
 class KVNeeds:
     """Keys and values in pages.  ``window`` None: every earlier key is read;
-    an integer w: a query at position p reads keys p-w+1 .. p."""
+    an integer w: a query at position p reads keys p-w+1 .. p.  ``dtype`` None: the engine's
+    activation dtype."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    dtype: torch.dtype | None = None
 
     @property
     def group_key(self) -> tuple:
-        return ("kv", self.num_kv_heads, self.head_dim, self.window)
+        return ("kv", self.num_kv_heads, self.head_dim, self.window, self.dtype)
 
 
 @dataclass(frozen=True)
 class StateNeeds:
-    """Per-request state of fixed size, kept in float32 in a slot of the slot pool."""
+    """Per-request state of fixed size, kept in a slot of the slot pool (float32 unless
+    ``dtype`` says otherwise)."""
 
     shape: tuple[int, ...]
+    dtype: torch.dtype | None = None
 
 
 @dataclass(frozen=True)
@@ -144,9 +154,23 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         """Receives the loaded tensors (same relative names) on the device."""
 
+    def step_arrays(self) -> dict[str, Callable]:
+        """Per-step int32 arrays this part's kernels read beside the common ones: name ->
+        builder ``StepPlan -> numpy int32 array`` (any shape).  The step layer builds them on the
+        host for every step, uploads them with the step's other arrays in the same transfer and
+        hands them over as ``inputs.extra[name]`` (device view of the same shape) and
+        ``inputs.plan.extra[name]`` (host).  Names are global to the model: parts that give the
+        same name must mean the same array (it is built once).  For a captured step to be
+        replayable a builder's output *shape* must follow from the step's sizes (tokens, rows,
+        wanted logits, table strides); an all-decode step is built on the plan padded to its
+        bucket."""
+        return {}
+
 
 class Norm(Part):
-    def forward(self, x32: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x32: torch.Tensor, out: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+        """The norm of ``x32``; with ``rows`` (int32 indices on the device) of those rows only."""
         raise NotImplementedError
 
     def as_epilogue(self, resid32: torch.Tensor):
@@ -156,8 +180,9 @@ class Norm(Part):
         return None
 
     def add_forward(self, resid32: torch.Tensor, delta: torch.Tensor | None,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
-        """resid32 += delta (in place, float32), then the norm of it."""
+                    out: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+        """resid32 += delta (in place, float32), then the norm of it.  With ``rows`` the norm of
+        ``resid32 + delta`` on those rows only, and the residual stream is left as it is."""
         raise NotImplementedError
 
 
@@ -189,6 +214,16 @@ class FeedForward(Part):
 
     def fusable(self, num_rows: int) -> bool:
         return False
+
+    def forward(self, x: torch.Tensor, inputs: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Stage(Part):
+    """A step of the model outside its layers: a scale or learned positions added after the token
+    table, a transform of the final hidden rows, a cap on the logits.  ``forward(x, inputs) -> x``
+    (it may work in place); where it stands says what ``x`` is (``ModelSpec.after_embedding``,
+    ``before_head``, ``after_head``)."""
 
     def forward(self, x: torch.Tensor, inputs: "Any") -> torch.Tensor:
         raise NotImplementedError
@@ -256,6 +291,7 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
+STAGES = Registry("model stage")
 
 
 def build_part(registry: Registry, spec: PartSpec, ctx: BuildContext, **extra):

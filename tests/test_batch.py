@@ -6,6 +6,7 @@ import torch
 from acorninfer_b200.cache.manager import CacheManager
 from acorninfer_b200.engine.batch import BatchError, StepEntry, StepWorkspace, plan_step, validate_entries
 from acorninfer_b200.engine.request import Request
+from acorninfer_b200.kernels.attention import STEP_ARRAYS
 from acorninfer_b200.parts.base import KVNeeds
 from acorninfer_b200.sampling.params import SamplingParams
 
@@ -46,7 +47,7 @@ def test_plan_of_a_mixed_step():
     entries = [StepEntry(a, [7], [0]), StepEntry(c, list(range(40)), [39, 0]), StepEntry(b, [3, 4], [])]
     for e in entries:
         m.extend(e.cache, e.cache.length + len(e.tokens))
-    plan = plan_step(entries, m)
+    plan = plan_step(entries, m, STEP_ARRAYS)
     assert plan.num_tokens == 43 and plan.num_rows == 3 and not plan.all_decode and plan.max_q_len == 40
     assert plan.token_ids.tolist() == [7] + list(range(40)) + [3, 4]
     assert plan.positions.tolist() == [9] + list(range(40)) + [70, 71]
@@ -54,9 +55,12 @@ def test_plan_of_a_mixed_step():
     assert plan.row_start.tolist() == [0, 1, 41, 43] and plan.row_pos.tolist() == [9, 0, 70]
     assert plan.row_slot.tolist() == [a.slot, c.slot, b.slot]
     assert plan.logit_tokens.tolist() == [0, 40, 1]              # entries in order, then `want` in order
-    assert plan.single_tokens.tolist() == [0]                   # the decoded token of a
-    assert plan.q_tiles.tolist() == [[1, 0], [2, 0]]            # rows with more than one token, 64 queries a tile
-    assert plan.q_tiles_large.tolist() == [[1, 0]] and plan.q_tiles_small.tolist() == [[2, 0]]
+    # the arrays the attention part declared are built by its builders, not by the step layer
+    x = plan.extra
+    assert x["attention.single_tokens"].tolist() == [0]                   # the decoded token of a
+    assert x["attention.q_tiles"].tolist() == [[1, 0], [2, 0]]            # rows with more than one token, 64 queries a tile
+    assert x["attention.q_tiles_large"].tolist() == [[1, 0]] and x["attention.q_tiles_small"].tolist() == [[2, 0]]
+    assert plan_step(entries, m).extra == {}                               # no part, no extra arrays
     full, win = plan.groups
     assert full.kv_len.tolist() == [10, 40, 72] and full.page_base.tolist() == [0, 0, 0]
     assert full.block_table.shape[1] >= 18 and full.block_table.shape[1] & (full.block_table.shape[1] - 1) == 0
@@ -77,7 +81,7 @@ def test_layout_depends_on_the_shape_only_and_is_aligned():
         entries = [StepEntry(rc, [t], [0]) for rc, t in zip(rcs, tokens)]
         for e in entries:
             m.extend(e.cache, e.cache.length + 1)
-        plan = plan_step(entries, m)
+        plan = plan_step(entries, m, STEP_ARRAYS)
         for e in entries:
             m.commit(e.cache, e.cache.length + 1)
         return plan
@@ -109,7 +113,7 @@ def test_decode_steps_are_padded_to_buckets_with_rows_that_touch_only_the_paddin
         m.commit(rc, 5 + i)
         entries.append(StepEntry(rc, [i + 1], [0] if i != 2 else []))
     plan = plan_step(entries, m)
-    padded = pad_decode_plan(plan, m.pad_page, m.pad_slot)
+    padded = pad_decode_plan(plan, m.pad_pages, m.pad_slot, STEP_ARRAYS)
     assert (plan.num_rows, plan.num_logits) == (5, 4) and (padded.num_rows, padded.num_logits) == (5, 4)
     entries.append(StepEntry(m.open(9), [7], [0]))
     m.extend(entries[-1].cache, 1)
@@ -118,13 +122,58 @@ def test_decode_steps_are_padded_to_buckets_with_rows_that_touch_only_the_paddin
         rc = m.open(20 + k)
         m.extend(rc, 1)
         entries.append(StepEntry(rc, [3], [0]))
-    plan = plan_step(entries, m)                       # 9 rows -> 10, 8 wanted -> 8
-    padded = pad_decode_plan(plan, m.pad_page, m.pad_slot)
+    plan = plan_step(entries, m, STEP_ARRAYS)          # 9 rows -> 10, 8 wanted -> 8
+    padded = pad_decode_plan(plan, m.pad_pages, m.pad_slot, STEP_ARRAYS)
     assert padded.num_rows == padded.num_tokens == 10 and padded.num_logits == 8 and padded.all_decode
     assert padded.token_ids[:9].tolist() == plan.token_ids.tolist() and padded.token_ids[9] == 0
     assert padded.positions[9] == 0 and padded.row_slot[9] == m.pad_slot == 16 and padded.row_pos[9] == 0
     g = padded.groups[0]
-    assert g.block_table[9, 0] == m.pad_page == 64 and g.kv_len[9] == 1
+    assert g.block_table[9, 0] == m.pad_pages[0] == 64 and g.kv_len[9] == 1
     assert g.block_table[:9].tolist() == plan.groups[0].block_table.tolist()
-    assert padded.row_start.tolist() == list(range(11)) and padded.single_tokens.tolist() == list(range(10))
+    assert padded.row_start.tolist() == list(range(11)) and padded.extra["attention.single_tokens"].tolist() == list(range(10))
     assert m.free_pages()[0] + sum(len(rc.tables[0]) for rc in m.live.values()) == 64   # the padding page is outside the pool
+
+
+def test_a_captured_step_finds_its_arrays_whatever_the_patch_lists_hold():
+    """Every array a captured decode step reads sits at an address that follows from the graph's key:
+    rows whose token ids come from the device (the patch lists) change no other array's place, for
+    every row count of a bucket, and the key tells buckets and table strides apart."""
+    from acorninfer_b200.engine.batch import decode_bucket, pad_decode_plan
+    m = CacheManager({0: KVNeeds(2, 16, None), 1: KVNeeds(2, 16, 6)}, {}, 256, 4, 64, dtype=torch.float32,
+                     device="cpu", allocate=False)
+    rcs = [m.open(i) for i in range(48)]
+    for rc in rcs:
+        m.extend(rc, 6)
+        m.commit(rc, 5)
+
+    def padded(R, patched):
+        entries = [StepEntry(rc, [1], [0], from_device=(i if i < patched else None)) for i, rc in enumerate(rcs[:R])]
+        plan = pad_decode_plan(plan_step(entries, m, STEP_ARRAYS), m.pad_pages, m.pad_slot, STEP_ARRAYS)
+        return plan
+
+    by_key = {}
+    for R in list(range(1, 9)) + list(range(33, 49)):
+        for patched in (0, 1, R // 2, R):
+            plan = padded(R, patched)
+            assert plan.patch_dst.size == patched and plan.num_rows == decode_bucket(R)
+            lay, total = StepWorkspace.layout(plan)
+            read_by_graph = {k: v for k, v in lay.items() if not k.startswith("patch_")}
+            assert all(lay[k][0] >= max(o + n for o, n in read_by_graph.values()) for k in ("patch_dst", "patch_src"))
+            key = StepWorkspace.shape_key(plan)
+            assert by_key.setdefault(key, read_by_graph) == read_by_graph, (R, patched)
+    assert len(by_key) == 8 + 2                                  # rows 1..8, buckets 40 and 48
+
+
+def test_a_step_that_cannot_be_uploaded_gives_its_pages_back():
+    m = manager()
+    a = m.open("a")
+    m.extend(a, 9)
+    m.commit(a, 6)                     # 3 pages held, 6 tokens committed (page size 4: 2 pages needed)
+    m.extend(a, 30)
+    assert len(a.tables[0]) == 8
+    m.trim(a)
+    assert len(a.tables[0]) == 2 and m.free_pages() == [62]
+    m.trim(a)                          # nothing more to give
+    assert len(a.tables[0]) == 2
+    m.close(a)
+    m.assert_balanced()

@@ -6,7 +6,7 @@ the same tokens; a request that can never fit is stopped)."""
 import pytest
 
 from tests.plain import model as plain
-from tests.tiny import TINY_A, TINY_B, TINY_C, make_model_dir, random_tokens, read_weights, sizes_of
+from tests.tiny import TINY_A, TINY_B, TINY_C, TINY_D, make_model_dir, random_tokens, read_weights, sizes_of
 
 pytestmark = pytest.mark.gpu
 
@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     out = {}
-    for name, tiny in (("a", TINY_A), ("b", TINY_B), ("c", TINY_C)):
+    for name, tiny in (("a", TINY_A), ("b", TINY_B), ("c", TINY_C), ("d", TINY_D)):
         d = make_model_dir(tmp_path_factory.mktemp(name), tiny)
         out[name] = (tiny, d, read_weights(d))
     return out
@@ -143,33 +143,107 @@ def test_command_line(folders, capsys):
                "--page-size", "4", "--num-blocks", "16"])
     out = capsys.readouterr().out.strip().splitlines()[-1]
     ids = [int(t) for t in out.split(",")]
-    assert rc == 0 and ids[:3] == [5, 6, 7] and 4 <= len(ids) <= 7
+    ref = plain.greedy_generate(sizes_of(tiny["cfg"]), w, [5, 6, 7], 4)
+    eos = set(tiny["cfg"].eos_token_id)
+    stop = next((i for i in range(3, len(ref)) if ref[i] in eos), len(ref) - 1)     # the configuration's eos ids apply
+    assert rc == 0 and (ids == ref[:stop + 1] or follows_plain(sizes_of(tiny["cfg"]), w, [5, 6, 7], ids, 1e-5))
+    assert len(ids) == stop + 1
+
+
+def run_engine(runner, prompts, lookahead, eos_ids, max_running=4, budget=11, watermark=1, base_tokens=9):
+    from acorninfer_b200.engine.engine import Engine
+    from acorninfer_b200.sampling.params import SamplingParams
+    eng = Engine(runner, max_running=max_running, watermark_blocks=watermark, chunked_budget=budget, lookahead=lookahead)
+    ids = []
+    for i, p in enumerate(prompts):
+        sp = SamplingParams(temperature=0.0) if i % 2 == 0 else SamplingParams(temperature=0.8, top_k=20, seed=i)
+        ids.append(eng.submit(p, sp, max_tokens=base_tokens + i % 7, eos_ids=eos_ids))
+    steps = 0
+    while eng.has_pending():
+        eng.step()
+        steps += 1
+        assert steps < 2000
+    eng.assert_balanced()
+    return [(eng.seqs[i].all_ids, eng.seqs[i].stop_reason) for i in ids], sum(eng.seqs[i].preemptions for i in ids)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_lookahead_gives_the_same_tokens_as_reading_every_step(folders, dtype):
     """One step ahead (ids stay on the device, the host reads them a call later) and step by step
     give the same sequences: greedy and sampled, with eos stops, a token budget and a tight pool."""
-    from acorninfer_b200.engine.engine import Engine
     from acorninfer_b200.engine.runner import ModelRunner
-    from acorninfer_b200.sampling.params import SamplingParams
     tiny, d, w = folders["b"]
     cfg = tiny["cfg"]
     prompts = [random_tokens(n, cfg.vocab_size, 300 + n) for n in (3, 17, 9, 26, 1, 12)]
-    results = {}
-    for lookahead in (False, True):
-        runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=14, page_size=8, max_requests=4)
-        eng = Engine(runner, max_running=4, watermark_blocks=1, chunked_budget=11, lookahead=lookahead)
-        ids = []
-        for i, p in enumerate(prompts):
-            sp = SamplingParams(temperature=0.0) if i % 2 == 0 else SamplingParams(temperature=0.8, top_k=20, seed=i)
-            ids.append(eng.submit(p, sp, max_tokens=9 + i, eos_ids=(5, 77, 130, 200, 310)))
-        steps = 0
-        while eng.has_pending():
-            eng.step()
-            steps += 1
-            assert steps < 500
-        results[lookahead] = [(eng.seqs[i].all_ids, eng.seqs[i].stop_reason) for i in ids]
-        eng.assert_balanced()
+    make = lambda: ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=14, page_size=8, max_requests=4)
+    # eos ids taken from what the requests generate when nothing stops them: some tokens from the
+    # middle of two generations, so that stops by eos (the wasted row of a step ahead) do happen
+    free_run, _ = run_engine(make(), prompts, False, ())
+    eos = (free_run[0][0][len(prompts[0]) + 4], free_run[3][0][len(prompts[3]) + 6])
+    results = {look: run_engine(make(), prompts, look, eos)[0] for look in (False, True)}
     assert results[True] == results[False]
-    assert any(reason == "stop" for _, reason in results[True]) or True
+    assert sum(reason == "stop" for _, reason in results[True]) >= 2
+    assert any(reason == "length" for _, reason in results[True])
+
+
+def test_a_warmed_runner_serves_a_lookahead_engine_and_a_step_by_step_engine_alike(folders):
+    """Graphs captured by ``warm_up`` (no row takes its id from the device) are replayed by an engine a
+    step ahead (every decoded row does), then by one that reads every step, on the same runner: the
+    place of every array a graph reads must not depend on how many ids come from the device."""
+    from acorninfer_b200.engine.runner import ModelRunner
+    tiny, d, w = folders["d"]
+    cfg = tiny["cfg"]
+    runner = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=96, page_size=16, max_requests=8)
+    runner.warm_up(prompt_tokens=(16,), decode_rows=(1, 2, 3, 4, 5, 6))
+    prompts = [random_tokens(n, cfg.vocab_size, 700 + n) for n in (5, 19, 33, 8, 27, 12)]
+    replays = runner.graph_replays
+    ahead, _ = run_engine(runner, prompts, True, (), max_running=6, budget=64, base_tokens=12)
+    assert runner.graph_replays > replays + 5
+    by_step, _ = run_engine(runner, prompts, False, (), max_running=6, budget=64, base_tokens=12)
+    assert ahead == by_step
+    cold = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=96, page_size=16, max_requests=8, decode_graph=False)
+    assert run_engine(cold, prompts, False, (), max_running=6, budget=64, base_tokens=12)[0] == by_step
+    for i in range(0, len(prompts), 2):                       # the greedy ones follow the plain model
+        assert follows_plain(sizes_of(cfg), w, prompts[i], by_step[i][0], 0.06)
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_more_than_32_requests_decode_together(folders, lookahead):
+    """44 requests at once: decode batches above 32 rows (buckets 40 and 48 with padding rows, library
+    products), a step ahead (ids from the device) and step by step; greedy ones against the plain model."""
+    from acorninfer_b200.engine.runner import ModelRunner
+    tiny, d, w = folders["d"]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(3 + (7 * i) % 18, cfg.vocab_size, 900 + i) for i in range(44)]
+    runner = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=44 * 3 + 8, page_size=16, max_requests=44)
+    got, _ = run_engine(runner, prompts, lookahead, (), max_running=44, budget=256, watermark=2, base_tokens=10)
+    assert runner.graph_replays >= 3 and any(key[1] >= 40 for key in runner._graphs)      # a bucket above 32 rows was captured
+    for i in range(0, len(prompts), 2):
+        assert follows_plain(sizes_of(cfg), w, prompts[i], got[i][0], 0.06), i
+    if lookahead:
+        ref_runner = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=44 * 3 + 8, page_size=16, max_requests=44)
+        assert got == run_engine(ref_runner, prompts, False, (), max_running=44, budget=256, watermark=2, base_tokens=10)[0]
+
+
+def test_preemption_and_recomputation_in_bfloat16_follow_the_plain_model(folders):
+    """A pool so tight that requests are preempted and recomputed, on the fast kernels (head size 128,
+    bfloat16, a step ahead): the greedy tokens are still the plain model's within rounding."""
+    from acorninfer_b200.engine.runner import ModelRunner
+    tiny, d, w = folders["d"]
+    cfg = tiny["cfg"]
+    prompts = [random_tokens(n, cfg.vocab_size, 1100 + n) for n in (40, 23, 35, 18, 29)]
+    runner = ModelRunner.from_model_dir(d, dtype="bfloat16", num_blocks=11, page_size=16, max_requests=4)
+    from acorninfer_b200.engine.engine import Engine
+    from acorninfer_b200.sampling.params import SamplingParams
+    eng = Engine(runner, max_running=4, watermark_blocks=0, chunked_budget=48, lookahead=True)
+    ids = [eng.submit(p, SamplingParams(temperature=0.0), max_tokens=40, eos_ids=()) for p in prompts]
+    steps = 0
+    while eng.has_pending():
+        eng.step()
+        steps += 1
+        assert steps < 2000
+    eng.assert_balanced()
+    assert sum(eng.seqs[i].preemptions for i in ids) >= 2
+    for i, p in zip(ids, prompts):
+        assert len(eng.seqs[i].all_ids) == len(p) + 40
+        assert follows_plain(sizes_of(cfg), w, p, eng.seqs[i].all_ids, 0.06), i

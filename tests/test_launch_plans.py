@@ -20,11 +20,13 @@ def test_decode_splits_stay_within_what_the_kernels_take():
 def test_decode_splits_follow_the_measured_cases():
     # few pairs: many CTAs in flight; a count just above a multiple of 296: shorter CTAs; a well
     # filled last wave: no split
-    assert decode_splits(1, 8, 4096) >= 16
-    assert decode_splits(8, 8, 4096) == 4
-    assert decode_splits(32, 8, 4096) == 1 and decode_splits(64, 8, 4096) == 1 and decode_splits(96, 8, 4096) == 1
-    assert decode_splits(40, 8, 4096) > 1 and decode_splits(20, 8, 4096) > 1 and decode_splits(80, 8, 4096) > 1
-    assert decode_splits(8, 8, 48) == 1              # a single chunk cannot be split
+    assert decode_splits(1, 8, 4096, 128) >= 16
+    assert decode_splits(8, 8, 4096, 128) == 4
+    assert decode_splits(32, 8, 4096, 128) == 1 and decode_splits(64, 8, 4096, 128) == 1 and decode_splits(96, 8, 4096, 128) == 1
+    assert decode_splits(40, 8, 4096, 128) > 1 and decode_splits(20, 8, 4096, 128) > 1 and decode_splits(80, 8, 4096, 128) > 1
+    assert decode_splits(8, 8, 48, 128) == 1              # a single chunk cannot be split
+    # the estimate is in bytes: a smaller head size makes a pair's keys cheaper, which never asks for more splits
+    assert decode_splits(8, 8, 4096, 32) <= decode_splits(8, 8, 4096, 128)
 
 
 def test_gemm_plans_are_valid_for_any_shape():

@@ -53,7 +53,7 @@ class MixerHarness:
         entries = [StepEntry(rc, [0] * x.shape[0], []) for rc, x in rows]
         for e in entries:
             self.manager.extend(e.cache, e.cache.length + len(e.tokens))
-        inputs = self.ws.upload(plan_step(entries, self.manager))
+        inputs = self.ws.upload(plan_step(entries, self.manager, self.mixer.step_arrays()))
         out = self.mixer.forward(torch.cat([x for _, x in rows]).contiguous(), inputs, self.cache)
         for e in entries:
             self.manager.commit(e.cache, e.cache.length + len(e.tokens))

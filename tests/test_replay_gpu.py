@@ -33,14 +33,26 @@ def tiny_case(request, tmp_path_factory):
     return tiny, d, reqs, ref
 
 
-def run_cut(tiny, model_dir, steps, dtype):
+def run_cut(tiny, model_dir, steps, dtype, max_requests=4, watch=None):
+    """Replays ``steps`` on a pool just large enough for the trace.  ``watch(session, msg)`` is called
+    after every step, before the step's ended requests are closed."""
     from acorninfer_b200.engine.runner import ModelRunner
     from acorninfer_b200.replay import TraceSession
 
     pool_tokens = traces.max_live_tokens(steps)
     runner = ModelRunner.from_model_dir(model_dir, dtype=dtype, num_blocks=-(-pool_tokens // tiny["page_size"]),
-                                        page_size=tiny["page_size"], max_requests=4, max_step_tokens=4096)
-    got = traces.collect(TraceSession(runner).step, steps)
+                                        page_size=tiny["page_size"], max_requests=max_requests, max_step_tokens=4096)
+    session = TraceSession(runner)
+
+    def step(msg):
+        if watch is None:
+            return session.step(msg)
+        out = session.step(dict(msg, end=[]))
+        watch(session, msg)
+        session.step({"entries": [], "end": msg["end"]})
+        return out
+
+    got = traces.collect(step, steps)
     runner.manager.assert_balanced()
     return got
 
@@ -67,11 +79,101 @@ def test_cuts_agree_with_each_other_float32(tiny_case):
 
 
 def test_mixed_trace_reuses_pages(tiny_case):
-    """The mixed trace's pool is smaller than the sum of all requests, so later requests
-    can only run on pages that earlier ones gave back."""
-    tiny, _, reqs, _ = tiny_case
+    """In the mixed trace physical pages really serve several requests one after another: seen on the
+    cache manager's block tables while the trace runs, whatever order the pool hands pages out in."""
+    tiny, d, reqs, _ = tiny_case
     steps = traces.mixed(reqs)
     assert traces.max_live_tokens(steps) < sum(-(-len(t) // 64) * 64 for t in reqs.values())
+    served: dict[int, set] = {}
+
+    def watch(session, msg):
+        for rid, rc in session.live.items():
+            for page in rc.tables[0]:
+                served.setdefault(page, set()).add(rid)
+
+    run_cut(tiny, d, steps, "float32", watch=watch)
+    assert sum(1 for users in served.values() if len(users) >= 2) >= 2, served
+
+
+# ------------------------------------------------------------------ schedules of a serving engine, head size 128
+
+
+@pytest.fixture(scope="module")
+def tiny_d_long(tmp_path_factory):
+    """Tiny D (head size 128: the tcgen05 prefill and TMA decode kernels) with requests long enough
+    for portions of 32 to 60 tokens that start inside a request and inside a 128-key block."""
+    tiny = TINIES["tiny_d"]
+    d = make_model_dir(tmp_path_factory.mktemp("tiny_d_long"), tiny)
+    w = read_weights(d)
+    reqs = {f"q{i}": random_tokens(n, tiny["cfg"].vocab_size, 2000 + i) for i, n in enumerate([230, 171, 140, 260, 97, 205])}
+    ref = {rid: plain.forward(sizes_of(tiny["cfg"]), w, toks).numpy() for rid, toks in reqs.items()}
+    return tiny, d, reqs, ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_beside_decoded_tokens(tiny_d_long, dtype):
+    """What a serving engine does at every step of a chunked prefill: portions of up to 60 tokens of
+    some requests (on the tcgen05 kernel from 32 tokens on, starting anywhere) in one step, and one
+    output tensor, with single decoded tokens of others (TMA decode kernel)."""
+    from acorninfer_b200.kernels import ops
+    tiny, d, reqs, ref = tiny_d_long
+    steps = traces.mixed(reqs, seed=3, prompt_frac=0.7, min_portion=20, max_portion=60, stagger=5)
+    both = [s for s in steps if any(len(e["tokens"]) >= 32 for e in s["entries"])
+            and any(len(e["tokens"]) == 1 for e in s["entries"])]
+    assert len(both) >= 5                                     # the trace has the steps this test is about
+    before = dict(ops.COUNTS)
+    got = run_cut(tiny, d, steps, dtype)
+    ran = {k: v - before.get(k, 0) for k, v in ops.COUNTS.items()}
+    if dtype == "bfloat16":
+        assert ran.get("attention_prefill_tc", 0) >= 10 and ran.get("attention_decode_tma", 0) >= 10
+        assert ran.get("attention_plain", 0) == 0
+    assert len(got) == sum(len(t) for t in reqs.values())
+    for (rid, pos), row in got.items():
+        diff = np.abs(row - ref[rid][pos]).max()
+        assert diff < TOL[dtype], f"{dtype}: request {rid} position {pos}: |d|={diff:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forty_requests_decoding(tmp_path_factory, dtype):
+    """A decode batch above 32 rows: the padded bucket of 40 (and 48 when 41 are live), its padding
+    rows, the library products with the residual as their C operand, the stand-alone norm / rotation /
+    SwiGLU kernels at decode shape and captured graphs, all against the plain model."""
+    tiny = TINIES["tiny_d"]
+    d = make_model_dir(tmp_path_factory.mktemp("forty"), tiny)
+    w = read_weights(d)
+    V = tiny["cfg"].vocab_size
+    reqs = {f"m{i}": random_tokens(14 + (5 * i) % 23, V, 3000 + i) for i in range(41)}
+    ref = {rid: plain.forward(sizes_of(tiny["cfg"]), w, toks).numpy() for rid, toks in reqs.items()}
+    steps, at = [], {rid: 0 for rid in reqs}
+    # prompts: all but the last 8 tokens of each request, five requests a step
+    rids = list(reqs)
+    for i in range(0, len(rids), 5):
+        entries = []
+        for rid in rids[i:i + 5]:
+            n = len(reqs[rid]) - 8
+            entries.append({"id": rid, "tokens": reqs[rid][:n], "want": [n - 1]})
+            at[rid] = n
+        steps.append({"entries": entries, "end": []})
+    # then every live request decodes: 41 rows (bucket 48) for one step, 40 rows (bucket 40) afterwards
+    for k in range(8):
+        live = rids if k == 0 else rids[:40]
+        entries = [{"id": rid, "tokens": [reqs[rid][at[rid]]], "want": [0]} for rid in live]
+        for rid in live:
+            at[rid] += 1
+        steps.append({"entries": entries, "end": [rids[40]] if k == 0 else []})
+    steps[-1]["end"] = rids[:40]
+    for i, s in enumerate(steps):
+        s["step"] = i
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.replay import TraceSession
+    runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=41 * 3 + 2, page_size=16, max_requests=41)
+    got = traces.collect(TraceSession(runner).step, steps)
+    runner.manager.assert_balanced()
+    assert runner.graph_replays >= 5                           # the bucket of 40 was captured and replayed
+    assert len(got) == 41 + 41 + 7 * 40
+    for (rid, pos), row in got.items():
+        diff = np.abs(row - ref[rid][pos]).max()
+        assert diff < TOL[dtype], f"{dtype}: request {rid} position {pos}: |d|={diff:.3e}"
 
 
 def test_weights_stored_in_float32_stay_float32_under_a_bfloat16_engine(tmp_path):

@@ -159,3 +159,42 @@ def test_random_load_never_exhausts_in_step_and_everything_finishes():
             assert guard < 5000
         assert all(len(r.generated_ids) == r.max_tokens for r in reqs)
         m.assert_balanced()
+
+
+def test_a_request_that_runs_no_more_gives_its_pages_up_first_and_is_not_queued_again():
+    """The engine runs a step ahead of the host: a request whose last allowed token is sampled but
+    not yet read (pending) still holds pages.  When pages run out it is the victim although an
+    older request runs, it is not queued for recomputation, and the older one keeps running."""
+    m, s = make(num_pages=4, page_size=4, max_running=3)
+    old, done = req(0, 8, max_tokens=8), req(1, 7, max_tokens=2)
+    s.add(old)
+    s.add(done)
+    run_step(m, s, s.schedule())                       # both prompts: 2 + 2 pages; each has its first token
+    assert m.free_pages() == [0] and s.running == [old, done]
+    done.pending = 1                                   # its second and last token is sampled, the host has not read it
+    assert done.exhausted and not done.is_finished
+    d = s.schedule()                                   # old's next token needs a third page
+    assert d.preempted == [done] and done not in s.waiting and done not in s.running and done.cache is None
+    assert done.preemptions == 0 and [(p.request, p.length) for p in d.portions] == [(old, 1)]
+    run_step(m, s, d)
+    done.pending = 0                                   # the host reads the token: finished, holding nothing
+    done.generated_ids.append(9)
+    done.status = RequestStatus.FINISHED
+    while s.has_pending():
+        run_step(m, s, s.schedule())
+    m.assert_balanced()
+
+
+def test_a_finished_request_does_not_block_the_queue():
+    """A preempted request that ended on the token still in flight (an eos id) must not sit at the
+    head of the queue: it is dropped and the next request is admitted."""
+    m, s = make(num_pages=8, page_size=4, max_running=2)
+    gone, nxt = req(0, 30, max_tokens=4), req(1, 5, max_tokens=2)
+    gone.status = RequestStatus.FINISHED               # needs 8 pages: it would block the queue for ever
+    s.waiting.appendleft(gone)
+    s.add(nxt)
+    d = s.schedule()
+    assert d.admitted == [nxt] and gone not in s.waiting
+    while s.has_pending():
+        run_step(m, s, s.schedule())
+    m.assert_balanced()

@@ -1,8 +1,10 @@
 """Another architecture, defined here and nowhere in the framework: a mixer with state of its
-own (a running mean over the request's tokens, kept in a state slot), a windowed attention
-layer beside it, a layer that runs twice and a run that reads another run's cache.  It is
+own (a running mean over the request's tokens, kept in a state slot) that reads a per-step array
+it declared itself, a windowed attention layer beside it, a layer that runs twice, a run that
+reads another run's cache, a scale after the token table and a cap on the logits.  It is
 registered, built from a model folder and stepped through the same runner and replay, cut in
-every way, and compared with a plain whole-sequence computation written here."""
+every way, and compared with a plain whole-sequence computation written here; its decode steps
+are captured and replayed as CUDA graphs like the built-in model's."""
 
 from dataclasses import dataclass
 from typing import ClassVar
@@ -12,8 +14,8 @@ import pytest
 import torch
 
 from acorninfer_b200.config.model_config import ModelConfig
-from acorninfer_b200.parts.base import (MIXERS, CacheNeeds, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry,
-                                        StateNeeds, TensorSpec)
+from acorninfer_b200.parts.base import (MIXERS, STAGES, CacheNeeds, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry,
+                                        Stage, StateNeeds, TensorSpec)
 from acorninfer_b200.registry import register_architecture, unregister_architecture
 from tests import traces
 from tests.plain import model as plain
@@ -34,6 +36,8 @@ class ToyConfig(ModelConfig):
     window: int = 9
     eps: float = 1e-5
     theta: float = 3e4
+    embedding_scale: float = 1.7
+    logit_cap: float = 1.5
 
     @classmethod
     def from_dict(cls, raw):
@@ -42,7 +46,14 @@ class ToyConfig(ModelConfig):
 
 class RunningMean(Mixer):
     """out[t] = W . mean(x[0..t]) over the tokens of the request so far.  The sum and the count
-    live in the request's state slot, so a portion continues where the last one stopped."""
+    live in the request's state slot, so a portion continues where the last one stopped.
+
+    Everything it needs of the step it reads on the device: the common arrays and one of its own,
+    ``toy.token_slot`` (the state slot of every token), declared through ``step_arrays`` and built
+    on the host by the step layer.  Nothing of the step is read on the host, so the mixer is
+    ``graph_safe`` and the model's decode steps can be captured."""
+
+    graph_safe = True
 
     def __init__(self, ctx, width):
         self.ctx, self.width, self.w = ctx, width, None
@@ -56,19 +67,54 @@ class RunningMean(Mixer):
     def cache_needs(self):
         return CacheNeeds(state=StateNeeds((self.width + 1,)))
 
+    def step_arrays(self):
+        return {"toy.token_slot": lambda plan: plan.row_slot[plan.token_row]}
+
     def forward(self, x, inputs, cache):
         from acorninfer_b200.kernels import ops
-        out = torch.empty_like(x)
-        plan = inputs.plan
-        for r in range(plan.num_rows):
-            a, b = int(plan.row_start[r]), int(plan.row_start[r + 1])
-            st = cache.state[int(plan.row_slot[r])]
-            sums = st[:self.width] + torch.cumsum(x[a:b].float(), dim=0)
-            counts = st[self.width] + torch.arange(1, b - a + 1, device=x.device, dtype=torch.float32)
-            out[a:b] = (sums / counts[:, None]).to(x.dtype)
-            st[:self.width] = sums[-1]
-            st[self.width] = counts[-1]
+        T = x.shape[0]
+        slot = inputs.extra["toy.token_slot"].long()                 # [T], on the device
+        row = inputs.token_row.long()
+        x32 = x.float()
+        # sum over the tokens of the same row up to and including each token, as a masked product
+        t = torch.arange(T, device=x.device)
+        mask = ((row[:, None] == row[None, :]) & (t[None, :] <= t[:, None])).float()
+        sums = cache.state[slot, :self.width] + mask @ x32
+        counts = cache.state[slot, self.width] + mask.sum(1)
+        out = (sums / counts[:, None]).to(x.dtype)
+        cache.state.index_add_(0, slot, torch.cat([x32, torch.ones(T, 1, device=x.device)], dim=1))
         return ops.linear(out, self.w, out_dtype=self.ctx.dtype)
+
+
+class ScaleRows(Stage):
+    """x * factor, after the token table."""
+
+    graph_safe = True
+
+    def __init__(self, ctx, factor):
+        self.factor = factor
+
+    def forward(self, x, inputs):
+        return x.mul_(self.factor)
+
+
+class SoftCap(Stage):
+    """cap * tanh(logits / cap), with a learned per-token bias on the logits to show that a stage
+    may own tensors."""
+
+    graph_safe = True
+
+    def __init__(self, ctx, cap, vocab):
+        self.cap, self.vocab, self.bias = cap, vocab, None
+
+    def tensor_specs(self):
+        return {"bias": TensorSpec((self.vocab,))}
+
+    def bind(self, tensors):
+        self.bias = tensors["bias"].float()
+
+    def forward(self, x, inputs):
+        return self.cap * torch.tanh((x + self.bias) / self.cap)
 
 
 def toy_spec(cfg: ToyConfig) -> ModelSpec:
@@ -94,7 +140,9 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
     schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, reads_cache_of=2))
     return ModelSpec(cfg.vocab_size, cfg.hidden_size, "model.embed_tokens.weight", layers, schedule,
                      PartSpec("rmsnorm", norm, "model.norm."), "lm_head.weight",
-                     {"rope": PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.theta})})
+                     {"rope": PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.theta})},
+                     after_embedding=(PartSpec("toy_scale", {"factor": cfg.embedding_scale}),),
+                     after_head=(PartSpec("toy_softcap", {"cap": cfg.logit_cap, "vocab": cfg.vocab_size}, "logit_cap."),))
 
 
 def toy_plain(cfg: ToyConfig, weights, ids):
@@ -104,7 +152,7 @@ def toy_plain(cfg: ToyConfig, weights, ids):
              "rms_norm_eps": cfg.eps, "rope_theta": cfg.theta}
     ids = torch.as_tensor(ids)
     pos = torch.arange(len(ids))
-    x = w["model.embed_tokens.weight"][ids]
+    x = w["model.embed_tokens.weight"][ids] * cfg.embedding_scale
     kv_of_entry = {}
     for entry, (layer, reads) in enumerate([(0, None), (1, None), (2, None), (1, None), (2, 2)]):
         p = f"model.layers.{layer}."
@@ -118,13 +166,16 @@ def toy_plain(cfg: ToyConfig, weights, ids):
             kv_of_entry[entry] = kv
         x = x + a
         x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg.eps), w, p + "mlp.")
-    return plain.rms_norm(x, w["model.norm.weight"], cfg.eps) @ w["lm_head.weight"].T
+    logits = plain.rms_norm(x, w["model.norm.weight"], cfg.eps) @ w["lm_head.weight"].T
+    return cfg.logit_cap * torch.tanh((logits + w["logit_cap.bias"]) / cfg.logit_cap)
 
 
 @pytest.fixture(scope="module")
 def toy(tmp_path_factory):
     from acorninfer_b200.weights.random_init import write_random_model
     MIXERS.register("toy_running_mean", RunningMean)
+    STAGES.register("toy_scale", ScaleRows)
+    STAGES.register("toy_softcap", SoftCap)
     register_architecture(ToyConfig.architecture, ToyConfig, toy_spec)
     cfg = ToyConfig()
     d = write_random_model(tmp_path_factory.mktemp("toy"), cfg, seed=9, sigma=0.08, sigma_norm=0.1)
@@ -146,8 +197,11 @@ def test_toy_architecture_runs_through_the_same_runner_and_replay(toy, dtype, to
         runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=-(-traces.max_live_tokens(steps) // 8),
                                             page_size=8, max_requests=4)
         assert len(runner.manager.groups) == 2 and len(runner.manager.state) == 1   # window, full; one state
+        assert runner.decode_graph and "toy.token_slot" in runner.step_arrays         # every part is graph_safe
         got = traces.collect(TraceSession(runner).step, steps)
         runner.manager.assert_balanced()
+        if cut == "decode_tail":
+            assert runner.graph_replays >= 5 * 29          # 32 single-token steps a request: seen, captured, replayed
         for (rid, pos), row in got.items():
             assert np.abs(row - ref[rid][pos]).max() < tol, (cut, rid, pos)
 

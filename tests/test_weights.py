@@ -104,3 +104,43 @@ def test_sharded_folder_with_index(tmp_path):
         {"weight_map": {n: ("s1.safetensors" if i < half else "s2.safetensors") for i, n in enumerate(names)}}))
     got = load_tensors(d, expected_tensors(spec_for(TINY_A["cfg"])), torch.bfloat16, "cpu")
     assert all(torch.equal(got[n], w[n]) for n in names)
+
+
+def test_counter_based_generator_three_ways_on_the_host():
+    """The NumPy restatement of the formula, the compiled host loop and row ranges agree bit for bit;
+    the values have the mean and spread asked for; tensors and seeds do not repeat each other."""
+    import numpy as np
+    from acorninfer_b200.parts.base import TensorSpec
+    from acorninfer_b200.weights.random_init import normal_numpy, random_tensor, tensor_key
+
+    for init, shape, dtype in (("matrix", (130, 77), torch.bfloat16), ("matrix", (9, 5, 3), torch.float32),
+                               ("norm", (301,), torch.bfloat16), ("norm", (64,), torch.float32),
+                               ("table", (7, 11), torch.int32)):
+        spec = TensorSpec(shape, init)
+        a = random_tensor("some.weight", spec, 17, 0.03, 0.2, dtype, "cpu", backend="numpy")
+        b = random_tensor("some.weight", spec, 17, 0.03, 0.2, dtype, "cpu", backend="host")
+        assert a.dtype == dtype and tuple(a.shape) == shape and torch.equal(a, b), (init, shape)
+        part = random_tensor("some.weight", spec, 17, 0.03, 0.2, dtype, "cpu", rows=(2, 6), backend="numpy")
+        assert torch.equal(part, a[2:6])
+        other = random_tensor("other.weight", spec, 17, 0.03, 0.2, dtype, "cpu", backend="numpy")
+        again = random_tensor("some.weight", spec, 18, 0.03, 0.2, dtype, "cpu", backend="numpy")
+        assert not torch.equal(a, other) and not torch.equal(a, again)
+    big = normal_numpy(tensor_key(3, "w"), 0, 200_000, 0.5, 0.0).astype(np.float64)
+    assert abs(big.mean()) < 0.005 and abs(big.std() - 0.5) < 0.005
+    assert abs(np.mean((big / big.std()) ** 4) - 2.85) < 0.05          # sum of eight uniforms: kurtosis 3 - 1.2 / 8
+    ones = random_tensor("n.weight", TensorSpec((50,), "norm"), 1, 0.02, 0.0, torch.bfloat16, "cpu")
+    assert torch.equal(ones, torch.ones(50, dtype=torch.bfloat16))
+
+
+def test_a_part_can_register_an_init_kind_of_its_own():
+    from acorninfer_b200.parts.base import TensorSpec
+    from acorninfer_b200.weights.random_init import INIT_KINDS, random_state
+
+    INIT_KINDS.register("test_decay", lambda d: torch.sigmoid(d.normal(1.0, 2.0).float()).to(d.dtype))
+    try:
+        t = random_state({"a.decay": TensorSpec((40,), "test_decay")}, 5, dtype=torch.float32)["a.decay"]
+        assert t.shape == (40,) and float(t.min()) > 0 and float(t.max()) < 1 and float(t.mean()) > 0.7
+    finally:
+        INIT_KINDS._items.pop("test_decay")
+    with pytest.raises(KeyError, match="unknown init kind 'nope'; known: matrix, norm, table"):
+        random_state({"a": TensorSpec((4,), "nope")}, 5)

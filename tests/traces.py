@@ -48,18 +48,22 @@ def portions(requests: dict[str, list[int]], sizes=(7, 2, 5, 3, 16, 2, 11, 4)) -
 
 
 def mixed(requests: dict[str, list[int]], max_live: int = 4, seed: int = 0, prompt_frac: float = 0.6,
-          max_portion: int = 9) -> list[dict]:
+          max_portion: int = 9, min_portion: int = 2, stagger: int = 0) -> list[dict]:
     """Up to ``max_live`` requests at a time: the first ``prompt_frac`` of each is fed in random
-    portions (>= 2 tokens where possible), the rest token by token, beside whatever the other
-    live requests bring; some steps leave a request out.  Requests start as others end, so
-    with a small pool their pages are the ones just given back."""
+    portions (``min_portion`` to ``max_portion`` tokens, >= 2 where possible), the rest token by
+    token, beside whatever the other live requests bring; some steps leave a request out.  Requests
+    start as others end, so with a small pool their pages are the ones just given back.  With
+    ``stagger`` a request starts no sooner than that many steps after the one before it, so that
+    prompts of some run beside decoded tokens of others."""
     rng = random.Random(seed)
     waiting = list(requests.items())
     live: dict[str, dict] = {}
     steps = []
+    last_start = -stagger
     while waiting or live:
-        while waiting and len(live) < max_live:
+        while waiting and len(live) < max_live and (len(steps) - last_start >= stagger or not live):
             rid, toks = waiting.pop(0)
+            last_start = len(steps)
             live[rid] = {"toks": toks, "at": 0, "prompt": max(1, int(len(toks) * prompt_frac))}
         entries, end = [], []
         for rid, st in list(live.items()):
@@ -67,7 +71,7 @@ def mixed(requests: dict[str, list[int]], max_live: int = 4, seed: int = 0, prom
                 continue                                    # left out of this step
             left_prompt = st["prompt"] - st["at"]
             if left_prompt > 0:
-                n = min(left_prompt, rng.randint(2, max_portion))
+                n = min(left_prompt, rng.randint(min_portion, max_portion))
                 if left_prompt - n == 1:
                     n += 1
             else:
