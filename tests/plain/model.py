@@ -105,16 +105,18 @@ def decoder_layer(x, w, i, sizes, positions, window=None, shared_kv=None):
     return x, kv
 
 
-def forward(sizes: dict, weights: dict, token_ids, dtype=torch.float64, schedule=None, windows=None) -> torch.Tensor:
-    """acorninfer/models/qwen3.py:491-518: embedding, the layers, final norm, output matrix
-    (the token table when tied).  Returns logits [S, vocab] for every position.
+def final_hidden(sizes: dict, weights: dict, token_ids, dtype=torch.float64, schedule=None, windows=None,
+                 embedded: torch.Tensor | None = None) -> torch.Tensor:
+    """acorninfer/models/qwen3.py:491-515: embedding, the layers, final norm.  Returns the normed
+    hidden rows [S, hidden] that the output matrix multiplies.
 
     ``schedule``: list of (layer, reads_cache_of_entry | None), default each layer once;
-    ``windows``: per layer, a window or None."""
+    ``windows``: per layer, a window or None; ``embedded``: the token table's rows of
+    ``token_ids`` [S, hidden], for a caller that does not hold the whole table."""
     w = {k: v.to(dtype) for k, v in weights.items()}
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(ids.numel())
-    x = w["model.embed_tokens.weight"][ids]
+    x = embedded.to(dtype) if embedded is not None else w["model.embed_tokens.weight"][ids]
     n_layers = sizes["num_hidden_layers"]
     schedule = schedule or [(i, None) for i in range(n_layers)]
     kvs = []
@@ -122,10 +124,16 @@ def forward(sizes: dict, weights: dict, token_ids, dtype=torch.float64, schedule
         window = windows[layer] if windows else None
         x, kv = decoder_layer(x, w, layer, sizes, positions, window, kvs[reads] if reads is not None else None)
         kvs.append(kv)
-    x = rms_norm(x, w["model.norm.weight"], sizes["rms_norm_eps"])
-    head = w["lm_head.weight"] if "lm_head.weight" in w and not sizes.get("tie_word_embeddings") \
-        else w["model.embed_tokens.weight"]
-    return x @ head.T
+    return rms_norm(x, w["model.norm.weight"], sizes["rms_norm_eps"])
+
+
+def forward(sizes: dict, weights: dict, token_ids, dtype=torch.float64, schedule=None, windows=None) -> torch.Tensor:
+    """acorninfer/models/qwen3.py:516-518: the output matrix (the token table when tied) on the
+    final hidden rows.  Returns logits [S, vocab] for every position."""
+    x = final_hidden(sizes, weights, token_ids, dtype, schedule, windows)
+    head = weights["lm_head.weight"] if "lm_head.weight" in weights and not sizes.get("tie_word_embeddings") \
+        else weights["model.embed_tokens.weight"]
+    return x @ head.to(dtype).T
 
 
 def greedy_generate(sizes, weights, prompt, max_new_tokens, eos_ids=(), dtype=torch.float64) -> list[int]:
