@@ -61,6 +61,8 @@ class Engine:
         self._inflight: _Inflight | None = None
         self._next_id = 0
         self.steps = 0
+        self.host_seconds = 0.0        # time spent deciding and launching (not waiting for results), over all steps
+        self.rows_launched = 0         # rows of all launched steps
 
     @classmethod
     def from_config(cls, cfg: EngineConfig) -> "Engine":
@@ -128,11 +130,13 @@ class Engine:
         row in the step already launched (its result is dropped); requests that end by length are
         not scheduled again.  Without lookahead every call returns its own step's tokens."""
         outputs: list[TokenOutput] = []
+        t0 = time.perf_counter()
         decision = self.scheduler.schedule()
         launched = None
         try:
             if decision.portions:
                 launched = self._launch(decision)
+                self.rows_launched += len(decision.portions)
             elif self._inflight is None and self.scheduler.waiting and not self.scheduler.running:
                 req = self.scheduler.waiting[0]
                 need = self.manager.peak_pages(req.num_tokens, self.scheduler.chunked_budget)
@@ -142,6 +146,7 @@ class Engine:
                     self._finish(req, "capacity")
                     last = req.generated_ids[-1] if req.generated_ids else -1
                     outputs.append(TokenOutput(req.seq_id, last, True, "capacity"))
+            self.host_seconds += time.perf_counter() - t0
             if self.lookahead:
                 previous, self._inflight = self._inflight, launched
             else:

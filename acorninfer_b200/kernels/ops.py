@@ -26,6 +26,12 @@ F32, BF16 = 0, 1
 
 
 def lib():
+    if _TIMER is not None and _lib is not None:
+        return _TimedLib(_lib)
+    return _load()
+
+
+def _load():
     global _lib
     if _lib is None:
         if not torch.cuda.is_available():
@@ -170,11 +176,79 @@ LAUNCHES = 0      # kernels of this library launched so far (for reports)
 COUNTS: dict[str, int] = {}    # the same by entry point: tests use it to see which kernel a path really took
 
 
-def _ok(code: int, what: str) -> None:
+class KernelTimer:
+    """Per-launch device times of everything launched while it is active (``with kernel_timer() as t``):
+    a CUDA event before and after every launch of this library, and around the library matrix products
+    of ``linear``.  The events keep kernels from overlapping (no programmatic dependent launch across
+    them) and nothing may be captured meanwhile, so the times are those of each kernel alone, in the
+    order and with the data of a real step.  ``records()`` gives ``[(entry point, tag, microseconds)]``
+    after a synchronize; the tag tells launches of one entry point apart (a product's M x N x K)."""
+
+    def __init__(self):
+        self._events: list = []
+        self._open = None
+
+    def begin(self) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._open = ev
+
+    def end(self, what: str, tag: str = "") -> None:
+        if self._open is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._events.append((what, tag, self._open, ev))
+        self._open = None
+
+    def records(self) -> list[tuple[str, str, float]]:
+        torch.cuda.synchronize()
+        return [(what, tag, a.elapsed_time(b) * 1e3) for what, tag, a, b in self._events]
+
+
+_TIMER: KernelTimer | None = None
+
+
+class kernel_timer:
+    def __enter__(self) -> KernelTimer:
+        global _TIMER
+        if _TIMER is not None:
+            raise KernelError("kernel_timer: already active")
+        _load()
+        _TIMER = KernelTimer()
+        return _TIMER
+
+    def __exit__(self, *exc) -> None:
+        global _TIMER
+        _TIMER = None
+
+
+class _TimedLib:
+    """The library while a timer is active: every entry point records the start event first (the end
+    event is recorded where the wrapper reports the launch, ``_ok``)."""
+
+    def __init__(self, library):
+        self._library = library
+
+    def __getattr__(self, name):
+        fn = getattr(self._library, name)
+        if not name.startswith("acorn_") or name.endswith(("_supported", "_error")):
+            return fn
+
+        def timed(*args):
+            if _TIMER is not None:
+                _TIMER.begin()
+            return fn(*args)
+        return timed
+
+
+def _ok(code: int, what: str, tag: str = "") -> None:
     global LAUNCHES
     if code == 0:
         LAUNCHES += 1
         COUNTS[what] = COUNTS.get(what, 0) + 1
+        if _TIMER is not None:
+            _TIMER.end(what, tag)
         return
     if code == 10001:
         raise KernelError(f"{what}: sizes or dtypes not supported by this kernel")
@@ -479,7 +553,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
         out = torch.empty((M, N), dtype=torch.float32, device=a.device)
     _check(out, "out", torch.float32, 2)
     _ok(lib().acorn_gemm_f32(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
-                             out.stride(0), M, N, K, _stream()), "gemm_f32")
+                             out.stride(0), M, N, K, _stream()), "gemm_f32", f"{M}x{N}x{K}")
     return out
 
 
@@ -613,7 +687,7 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
         ep.positions.data_ptr(), _ptr(ep.token_row), _ptr(ep.block_table), _ptr(ep.page_base),
         ep.block_table.stride(0) if ep.block_table is not None else 0, _ptr(ep.k_pages), _ptr(ep.v_pages),
         _ptr(ep.q_weight32), _ptr(ep.k_weight32), ep.inv_freq.data_ptr(), nq, nkv, P, float(ep.eps), _stream()),
-        "gemm_tc_qkv_rope")
+        "gemm_tc_qkv_rope", f"{M}x{N}x{K}")
     return out
 
 
@@ -666,7 +740,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
         1 if out_dtype == torch.float32 else 0, int(splits), int(per_sm), mode,
         rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
         rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
-        _ptr(resid), ldr, _ptr(norm_w), _ptr(ss_out), _stream()), "gemm_tc")
+        _ptr(resid), ldr, _ptr(norm_w), _ptr(ss_out), _stream()), "gemm_tc", f"{M}x{N}x{K}")
     if epilogue is not None:
         return NormedRows(out, ss_out, epilogue.eps, N)
     return out
@@ -712,13 +786,19 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
         raise KernelError(f"linear: unsupported dtypes x={x.dtype}, w={w.dtype}")
     if x.shape[0] <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w):
         return gemm_tc(x, w, out_dtype)
-    if residual32 is not None and residual32.dtype == torch.float32 and residual32.is_contiguous() \
-            and tuple(residual32.shape) == (x.shape[0], w.shape[0]):
-        torch.addmm(residual32, x, w.t(), out_dtype=torch.float32, out=residual32)
-        return None
-    if out_dtype == torch.float32:
-        return torch.mm(x, w.t(), out_dtype=torch.float32)
-    return torch.mm(x, w.t())
+    if _TIMER is not None:
+        _TIMER.begin()
+    try:
+        if residual32 is not None and residual32.dtype == torch.float32 and residual32.is_contiguous() \
+                and tuple(residual32.shape) == (x.shape[0], w.shape[0]):
+            torch.addmm(residual32, x, w.t(), out_dtype=torch.float32, out=residual32)
+            return None
+        if out_dtype == torch.float32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.mm(x, w.t())
+    finally:
+        if _TIMER is not None:
+            _TIMER.end("library_gemm", f"{x.shape[0]}x{w.shape[0]}x{x.shape[1]}")
 
 
 # ------------------------------------------------------------------ sampling

@@ -35,6 +35,16 @@ PROMPT = 2048
 PAGE = 16
 
 
+def shared_config(args, peaks_source: str) -> dict:
+    """The workload, printed alike by both arms (flat, at most 20 keys)."""
+    return {"model": "Qwen3-8B sizes, random weights", "layers": args.layers,
+            "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": 4096, "q_heads": 32, "kv_heads": 8,
+            "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": args.batch,
+            "seq_len": CONTEXT, "prompt": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": peaks_source,
+            "kv": "device-timed value: synthetic pages (random K and V at full context); e2e: prompts prefilled by the engine under test"}
+
+
 def peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.is_file():
@@ -214,6 +224,162 @@ def time_e2e(runner, B: int, steps: int, warmup: int, ctx_end: int, torch):
             "h2d_bytes_per_step": 4 * lay_ints + 8 * 5 * B + 16 * B, "d2h_bytes_per_step": 4 * B}
 
 
+def _mean_by_tag(records) -> dict:
+    acc: dict = {}
+    for what, tag, us in records:
+        e = acc.setdefault((what, tag), [0, 0.0])
+        e[0] += 1
+        e[1] += us
+    return {k: (n, total / n) for k, (n, total) in acc.items()}
+
+
+def kernel_table(runner, nums: dict, conf: dict, B: int, ctx: int, T: int, pk: dict, torch) -> dict:
+    """Every launch of one decode step (batch B at context ctx) and of one prefill step (T tokens),
+    each timed alone with CUDA events in an eager step; the products, attention and the output
+    matrix with the bytes they must read or the flops they do, against the measured peaks."""
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.kernels import ops
+
+    H, nq, nkv, d, I, V = (conf["hidden_size"], conf["num_attention_heads"], conf["num_key_value_heads"],
+                           conf["head_dim"], conf["intermediate_size"], conf["vocab_size"])
+    hbm, tf = pk["hbm_gbs"], pk["bf16_tflops"]
+    graphs, runner.decode_graph = runner.decode_graph, False
+
+    def run_ahead():
+        """Keeps the device busy for some 20 ms so that the host has queued the whole step before its
+        first kernel starts: the events then bracket device time, not the host's launch latency."""
+        torch.cuda.synchronize()
+        torch.cuda._sleep(40_000_000)
+
+    try:
+        reqs = synthetic_requests(runner, B, ctx - 4, "kt")
+        step = lambda: runner.step([StepEntry(rc, [7], [0]) for rc in reqs])
+        step()
+        run_ahead()
+        with ops.kernel_timer() as timer:
+            step()
+        dec = _mean_by_tag(timer.records())
+        for rc in reqs:
+            runner.close(rc)
+        rc = runner.open("ktp")
+        g = torch.Generator().manual_seed(11)
+        toks = torch.randint(0, runner.vocab_size, (T,), generator=g).tolist()
+        run_ahead()
+        with ops.kernel_timer() as timer:
+            runner.step([StepEntry(rc, toks, [T - 1])])
+        pre = _mean_by_tag(timer.records())
+        runner.close(rc)
+    finally:
+        runner.decode_graph = graphs
+
+    def mem(key, nbytes):
+        n, us = dec.get(key, (0, None))
+        if us is None:
+            return {"us": None}
+        gbs = nbytes / us / 1e3
+        return {"us": round(us, 2), "calls": n, "MB": round(nbytes / 1e6, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / hbm, 3)}
+
+    def flop(key, flops):
+        n, us = pre.get(key, (0, None))
+        if us is None:
+            return {"us": None}
+        t = flops / us / 1e6
+        return {"us": round(us, 1), "calls": n, "TFLOPS": round(t, 1), "frac_bf16": round(t / tf, 3)}
+
+    qkv_n = (nq + 2 * nkv) * d
+    decode = {
+        "qkv_norm_rope_kvwrite": mem(("gemm_tc_qkv_rope", f"{B}x{qkv_n}x{H}"), 2 * qkv_n * H),
+        "attention_decode": mem(("attention_decode_tma", ""), 2 * 2 * B * ctx * nkv * d),
+        "attention_merge": {"us": round(dec.get(("attention_decode_merge", ""), (0, 0.0))[1], 2)},
+        "o_add_norm": mem(("gemm_tc", f"{B}x{H}x{nq * d}"), 2 * H * nq * d),
+        "gate_up_swiglu": mem(("gemm_tc", f"{B}x{2 * I}x{H}"), 2 * 2 * I * H),
+        "down_add_norm": mem(("gemm_tc", f"{B}x{H}x{I}"), 2 * H * I),
+        "lm_head": mem(("gemm_tc", f"{B}x{V}x{H}"), 2 * V * H),
+        "sum_us_layer": round(sum(us for (what, tag), (n, us) in dec.items()
+                                  if what.startswith(("gemm_tc", "attention")) and not tag.startswith(f"{B}x{V}x")), 1),
+    }
+    prefill = {
+        "attention_prefill": flop(("attention_prefill_tc", ""), nq * d * 4.0 * (T * (T + 1) / 2)),
+        "qkv_library": flop(("library_gemm", f"{T}x{qkv_n}x{H}"), 2.0 * T * qkv_n * H),
+        "o_library": flop(("library_gemm", f"{T}x{H}x{nq * d}"), 2.0 * T * H * nq * d),
+        "gate_up_library": flop(("library_gemm", f"{T}x{2 * I}x{H}"), 2.0 * T * 2 * I * H),
+        "down_library": flop(("library_gemm", f"{T}x{H}x{I}"), 2.0 * T * H * I),
+        "other_own_kernels_us": round(sum(us for (what, tag), (n, us) in pre.items()
+                                          if what in ("add_rmsnorm", "swiglu", "qk_rope_kv")), 1),
+    }
+    return {"timing": "CUDA events around each launch of one eager step queued behind a busy device: each kernel alone "
+                      "(in the captured step they overlap through programmatic dependent launch), mean over the layers",
+            f"decode_b{B}_ctx{ctx}": decode, f"prefill_{T}": prefill}
+
+
+def continuous_batching(torch) -> dict:
+    """Qwen3-0.6B layer sizes, 128 requests arriving at once (prompts uniform in 16..1,024, outputs in
+    16..512), token budget 2,048 a step, through ``Engine.submit/step``.  Run twice; the second run
+    (graphs and library kernels warm) is timed by the wall clock."""
+    from acorninfer_b200.bench import random_prompts
+    from acorninfer_b200.config.presets import preset
+    from acorninfer_b200.engine.engine import Engine
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.registry import config_from_dict
+    from acorninfer_b200.sampling.params import SamplingParams
+
+    n_req, budget = 128, 2048
+    cfg = config_from_dict(preset("qwen3-0.6b"))
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", num_blocks=n_req * (1024 + 512) // PAGE + 64,
+                                     page_size=PAGE, max_requests=n_req, max_step_tokens=budget)
+    gen = torch.Generator().manual_seed(4)
+    lens = torch.randint(16, 1025, (n_req,), generator=gen).tolist()
+    outs = torch.randint(16, 513, (n_req,), generator=gen).tolist()
+    prompts = random_prompts(n_req, lens, runner.vocab_size, 4)
+    result = {}
+    for timed in (False, True):
+        engine = Engine(runner, max_running=n_req, watermark_blocks=8, chunked_budget=budget, default_eos_ids=())
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        sids = [engine.submit(p, SamplingParams(temperature=0.0), max_tokens=n, eos_ids=()) for p, n in zip(prompts, outs)]
+        while engine.has_pending():
+            engine.step()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        total = sum(len(engine.seqs[i].generated_ids) for i in sids)
+        assert total == sum(outs)
+        for i in sids:
+            engine.drop(i)
+        engine.assert_balanced()
+        result = {"model": "Qwen3-0.6B sizes, random weights, bf16", "requests": n_req, "token_budget": budget,
+                  "prompt_tokens": sum(lens), "output_tokens": total, "output_tok_s": round(total / wall, 1),
+                  "total_tok_s": round((total + sum(lens)) / wall, 1), "wall_s": round(wall, 3), "steps": engine.steps,
+                  "mean_rows_per_step": round(engine.rows_launched / max(engine.steps, 1), 1),
+                  "host_ms_per_step": round(engine.host_seconds / max(engine.steps, 1) * 1e3, 3),
+                  "ms_per_step": round(wall / max(engine.steps, 1) * 1e3, 3)}
+    del engine, runner
+    return result
+
+
+def long_context(steps: int, warmup: int, pk: dict, torch) -> dict:
+    """Qwen3-32B layer sizes (64 layers, 65.5 GB of bfloat16 weights), 8 requests at context 16,384:
+    device-timed decode steps on synthetic pages, and the fraction of the memory roofline."""
+    from acorninfer_b200.config.presets import preset
+    from acorninfer_b200.engine.runner import ModelRunner
+    from acorninfer_b200.registry import config_from_dict
+
+    raw = preset("qwen3-32b")
+    cfg = config_from_dict(raw)
+    B, ctx = 8, 16384
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", num_blocks=B * ctx // PAGE + 64, page_size=PAGE,
+                                     max_requests=B + 1, max_step_tokens=4096)
+    for g in runner.manager.groups:
+        g.storage.normal_(0, 1)
+    nums = model_numbers(raw, raw["num_hidden_layers"])
+    res = time_decode(runner, None, B, steps, warmup, ctx, torch)
+    step_bytes = nums["weight_bytes"] + B * res["mean_context"] * nums["kv_bytes_per_token"]
+    gbs = step_bytes / (res["ms_per_step"] / 1e3) / 1e9
+    del runner
+    return {"model": "Qwen3-32B sizes, random weights, bf16", "layers": raw["num_hidden_layers"], "batch": B,
+            "context": ctx, "ms_per_step": round(res["ms_per_step"], 3), "tok_s": round(res["tok_s"], 1),
+            "step_GB": round(step_bytes / 1e9, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 4)}
+
+
 def reference_arm(args) -> int:
     """The unmodified reference (installed under baseline/_ref) through its own public API:
     ``from_pretrained`` + ``Engine.submit/step`` with its fastest documented settings (Triton paged
@@ -280,13 +446,23 @@ def reference_arm(args) -> int:
         torch.cuda.synchronize()
         ms = max(start.elapsed_time(end), (time.perf_counter() - t0) * 1e3)
         clock_info = clocks.stop()
+        # What its decode step copies, counted from its own staging tensors: two pinned blocks to the
+        # device (ids, positions, page and slot targets; lengths and block tables), one argmax list back.
+        h2d = d2h = None
+        runner_ = getattr(engine, "graph_runner", None)
+        if runner_ is not None:
+            st = runner_.states[min(b for b in runner_.states if b >= B)]
+            h2d = st.pin_long.numel() * st.pin_long.element_size() + st.pin_i32.numel() * st.pin_i32.element_size()
+            d2h = 8 * B
         line = {"impl": "reference", "metric": "decode tok/s at batch 8, context 4096 (Qwen3-8B layer sizes, 1 B200)",
                 "value": round(produced / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
                 "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"model": "Qwen3-8B sizes, random weights", "layers": args.layers, "global_batch": B,
-                           "seq_len": CONTEXT, "page_size": PAGE, "settings": "triton attention, fused ops, decode graph"},
-                "e2e": {"value": round(produced / (ms / 1e3), 1), "unit": "tokens/s"}, "clocks": clock_info}
+                "config": shared_config(args, peaks()["source"]),
+                "settings": "triton attention, fused ops, decode graph",
+                "e2e": {"value": round(produced / (ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms / steps, 4),
+                        "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "clocks": clock_info}
         print(json.dumps(line))
     except Exception as exc:  # the reference could not run here: say why, in one line
         reason = f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]
@@ -306,6 +482,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the batch of the headline value")
+    ap.add_argument("--skip-extra", action="store_true",
+                    help="leave out the per-kernel table, the continuous-batching run and the long-context run")
     args = ap.parse_args()
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
@@ -347,6 +525,19 @@ def main() -> int:
             points[f"decode_b{b}_ctx3072"] = round(time_decode(runner, sampler, b, args.steps, args.warmup, mid, torch)["tok_s"], 1)
     pre_ms = time_prefill(runner, PROMPT, 3, torch)
     e2e = time_e2e(runner, args.batch, args.steps, args.warmup, CONTEXT, torch)
+    extra = {}
+    if not args.skip_extra:
+        extra["kernels"] = kernel_table(runner, nums, conf, args.batch, CONTEXT, PROMPT, pk, torch)
+        del runner                      # the other workloads build models of their own: free this one's memory first
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        extra["continuous_batching"] = continuous_batching(torch)
+        gc.collect()
+        torch.cuda.empty_cache()
+        extra["long_context"] = long_context(min(args.steps, 32), 4, pk, torch)
+        points["cb_0.6b_128req_output_tok_s"] = extra["continuous_batching"]["output_tok_s"]
+        points["decode_32b_b8_ctx16384"] = extra["long_context"]["tok_s"]
 
     step_bytes = nums["weight_bytes"] + args.batch * head["mean_context"] * nums["kv_bytes_per_token"]
     achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
@@ -356,11 +547,8 @@ def main() -> int:
         "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(head["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Qwen3-8B sizes, random weights", "layers": args.layers,
-                   "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": 4096, "q_heads": 32, "kv_heads": 8,
-                   "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "prompt": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": pk["source"]},
+        "config": shared_config(args, pk["source"]),
+        "settings": "lookahead engine, captured decode steps, tcgen05 products up to 32 rows",
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": head["launches"],
         "prefill": {"value": round(PROMPT / (pre_ms / 1e3), 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
@@ -369,6 +557,7 @@ def main() -> int:
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "clocks": clock_info,
+        **extra,
     }
     print(json.dumps(line))
     return 0

@@ -145,6 +145,8 @@ def test_block_arrangement_part_float32():
     rc = hz.manager.open("a")
 
     class BlockAsMixer:
+        step_arrays = mixer.step_arrays
+
         def forward(self, xin, inputs, cache):
             resid, delta = block.forward(xin.float().clone(), None, inputs, cache)
             return resid + delta.float()

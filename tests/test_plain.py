@@ -55,3 +55,17 @@ def test_plain_sampling_processing():
     assert not torch.isinf(p[1])
     tok, lp, _ = plain.sample_with_uniform(plain.process_logits(x, 1.0), 0.0)
     assert tok == 0 and lp < 0
+
+
+def test_plain_sampling_processing_matches_the_reference_sampler():
+    """``process_logits`` against what the reference's own ``Sampler.process`` kept and left, for a
+    dozen settings (tests/golden/make_sampler_golden.py wrote the file from the reference's code)."""
+    cases = json.loads((Path(__file__).parent / "golden" / "sampler_reference_processing.json").read_text())
+    assert len(cases) >= 12
+    for c in cases:
+        logits = torch.tensor([float(x) for x in c["logits"]], dtype=torch.float32)
+        got = plain.process_logits(logits, c["temperature"], c["top_k"], c["top_p"])
+        kept = torch.isfinite(got).nonzero().flatten().tolist()
+        assert kept == c["kept"], (c["temperature"], c["top_k"], c["top_p"])
+        want = torch.tensor([float(x) for x in c["processed_kept"]], dtype=torch.float64)
+        assert (got[kept] - want).abs().max() < 1e-6

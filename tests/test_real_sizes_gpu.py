@@ -25,7 +25,8 @@ pytestmark = pytest.mark.gpu
 
 LAYERS, LAYERS_OF_CONFIG = 2, 36
 SEED, SIGMA, SIGMA_NORM = 8, 0.02, 0.1
-TOL = {"float32": 2e-5, "bfloat16": 8e-2}
+TOL = {"float32": 1e-4, "bfloat16": 1e-1}
+RMS_TOL = {"float32": 1e-5, "bfloat16": 2e-2}
 
 
 def config():
@@ -89,8 +90,18 @@ def runner(request):
     r.manager.assert_balanced()
 
 
-def worst(got, want):
-    return float(np.abs(got.double().cpu().numpy() - want).max())
+def check(got, want, dtype: str, what: str) -> None:
+    """The largest difference of any logit, and the root-mean-square difference relative to the logits'
+    own (a single wrong key or page moves far more than rounding does)."""
+    diff = got.double().cpu().numpy() - want
+    w = float(np.abs(diff).max())
+    rel = float(np.sqrt((diff ** 2).mean() / (want ** 2).mean()))
+    print(f"{what} [{dtype}]: worst |d| = {w:.3e}, rms(d) / rms(logits) = {rel:.3e}")
+    assert w < TOL[dtype] and rel < RMS_TOL[dtype], f"{what}: worst |d| = {w:.3e}, relative rms = {rel:.3e}"
+
+
+def dtype_of(runner) -> str:
+    return "float32" if runner.dtype == torch.float32 else "bfloat16"
 
 
 def test_sizes_are_the_benchmarks():
@@ -107,14 +118,13 @@ def test_a_prompt_whole_and_in_portions(runner, plain64):
     """300 tokens in one step; and as 200 + 60 + 40, where the second and third portions start inside
     the request and inside a block of 128 keys (tcgen05 attention with an offset)."""
     from acorninfer_b200.engine.batch import StepEntry
-    dtype = "float32" if runner.dtype == torch.float32 else "bfloat16"
     ids = random_tokens(300, runner.vocab_size, 41)
     places = [0, 1, 127, 128, 199, 200, 259, 260, 299]
     want = plain64.logits(ids, places)
     rc = runner.open("whole")
     got = runner.step([StepEntry(rc, ids, places)])
     runner.close(rc)
-    assert worst(got, want) < TOL[dtype], f"whole: {worst(got, want):.3e}"
+    check(got, want, dtype_of(runner), "whole")
     rc = runner.open("portions")
     parts, at = [], 0
     for n in (200, 60, 40):
@@ -122,8 +132,7 @@ def test_a_prompt_whole_and_in_portions(runner, plain64):
         parts.append(runner.step([StepEntry(rc, ids[at:at + n], mine)]))
         at += n
     runner.close(rc)
-    got = torch.cat(parts)
-    assert worst(got, want) < TOL[dtype], f"portions: {worst(got, want):.3e}"
+    check(torch.cat(parts), want, dtype_of(runner), "portions 200 + 60 + 40")
 
 
 def decode_case(runner, side, rows, prompt_lens, steps, seed):
@@ -141,7 +150,7 @@ def decode_case(runner, side, rows, prompt_lens, steps, seed):
         runner.close(rc)
     want = side.head_logits(torch.cat([side.hidden(s, range(len(s) - steps, len(s))) for s in seqs]))
     mine = torch.stack([got[k][j] for j in range(rows) for k in range(steps)])
-    return worst(mine, want)
+    check(mine, want, dtype_of(runner), f"{rows} requests decoding")
 
 
 def test_eight_requests_decoding(runner, plain64):
@@ -149,12 +158,10 @@ def test_eight_requests_decoding(runner, plain64):
     the residual sum and norm; gate/up with SwiGLU as half tiles; down split over a cluster at
     K = 12,288; the output matrix at N = 151,936), TMA decode attention in several splits, captured."""
     from acorninfer_b200.kernels.ops import gemm_tc_plan
-    dtype = "float32" if runner.dtype == torch.float32 else "bfloat16"
     assert gemm_tc_plan(8, 24576, 4096) == (2, 3) and gemm_tc_plan(8, 4096, 12288)[0] >= 2
     replays = runner.graph_replays
-    err = decode_case(runner, plain64, 8, (300, 41, 130, 257, 64, 199, 17, 90), 5, 500)
+    decode_case(runner, plain64, 8, (300, 41, 130, 257, 64, 199, 17, 90), 5, 500)
     assert runner.graph_replays >= replays + 3
-    assert err < TOL[dtype], f"{err:.3e}"
 
 
 @pytest.mark.parametrize("rows", [40, 64])
@@ -163,5 +170,4 @@ def test_many_requests_decoding(runner, plain32, rows):
     buckets of 40 and 64 rows, the decode kernel's splits for that many rows."""
     if runner.dtype == torch.float32:
         pytest.skip("the float32 engine has one path for every row count; it is checked at 8 rows")
-    err = decode_case(runner, plain32, rows, (21, 33, 18, 40, 27), 3, 7000 + rows)
-    assert err < TOL["bfloat16"], f"{err:.3e}"
+    decode_case(runner, plain32, rows, (21, 33, 18, 40, 27), 3, 7000 + rows)

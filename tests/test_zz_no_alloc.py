@@ -5,8 +5,9 @@ its scratch from the caller.  Such callers exist (a process under a fixed memory
 running where cudaMalloc is not allowed); for them the test also checks that a request beyond
 the fixed array is refused with a readable message instead of computing anything.
 
-This file sorts last on purpose: it is the newest addition, and a run that stops at the first
-failure has then already run everything else.
+Its result is also compared with a float64 computation of the same attention written here, so the
+file stands on its own.  The file's name makes pytest collect it last: a run that stops at the first
+failure has then already run every other test.
 """
 
 import ctypes
@@ -15,7 +16,7 @@ from ctypes import c_float, c_int, c_int64, c_void_p
 import pytest
 import torch
 
-from tests.paged import rows_layout
+from tests.paged import gather_from_pages, rows_layout
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -45,6 +46,20 @@ def case(before, nq, nkv, d, P, seed):
     return lay, qkv, k_pages, v_pages
 
 
+def dense_float64(lay, qkv, k_pages, v_pages, before, nq, nkv, d, P):
+    """Softmax attention of each row's single query over all its keys, in float64 on the host."""
+    out = torch.empty(len(before), nq * d, dtype=torch.float64)
+    for r, b in enumerate(before):
+        k = gather_from_pages(k_pages.cpu(), lay["tables"][r], b + 1, P).double()     # [S, nkv, d]
+        v = gather_from_pages(v_pages.cpu(), lay["tables"][r], b + 1, P).double()
+        q = qkv[r, :nq * d].cpu().double().view(nq, d)
+        for h in range(nq):
+            g = h // (nq // nkv)
+            p = torch.softmax((k[:, g] @ q[h]) * d ** -0.5, dim=0)
+            out[r, h * d:(h + 1) * d] = p @ v[:, g]
+    return out
+
+
 def run_both(lib, lay, qkv, k_pages, v_pages, nq, nkv, d, splits):
     from acorninfer_b200.kernels import ops
     n = qkv.shape[0]
@@ -63,16 +78,19 @@ def run_both(lib, lay, qkv, k_pages, v_pages, nq, nkv, d, splits):
 def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     lib = library()
     # first call: long rows, many splits (fills much of the scratch)
-    a = case([900, 64, 2047, 1, 500, 333], 32, 8, 128, 16, seed=1)
+    before = [900, 64, 2047, 1, 500, 333]
+    a = case(before, 32, 8, 128, 16, seed=1)
     rc, got, want = run_both(lib, *a, 32, 8, 128, 8)
     assert rc == 0, lib.acorn_noalloc_last_error()
     assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2) and torch.equal(got, want)
+    assert torch.allclose(got.double().cpu(), dense_float64(*a, before, 32, 8, 128, 16), atol=2e-2, rtol=2e-2)
     # second call right after: other sizes, fewer splits, short rows whose later splits are empty;
     # what the first call left in the scratch must not matter
     b = case([10, 70, 3], 10, 2, 48, 8, seed=2)
     rc, got, want = run_both(lib, *b, 10, 2, 48, 5)
     assert rc == 0, lib.acorn_noalloc_last_error()
     assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2) and torch.equal(got, want)
+    assert torch.allclose(got.double().cpu(), dense_float64(*b, [10, 70, 3], 10, 2, 48, 8), atol=2e-2, rtol=2e-2)
     # one split needs no scratch at all
     rc, got, want = run_both(lib, *b, 10, 2, 48, 1)
     assert rc == 0 and torch.equal(got, want)
