@@ -108,10 +108,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_prefill_tc_kernel(co
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + ATC_NUM_BARS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Tiles are listed by rising position within a request; the late tiles read the most keys, so
-    // they are started first.  CTAs next to one another share a key/value head (and tile).
+    // CTAs are started in the order of the tile list, which the caller sorts by falling number of keys
+    // a tile reads: the long tiles first, the short ones fill the tail of the last wave.  CTAs next
+    // to one another share a tile and mostly a key/value head.
     const int per_tile = p.nkv * p.pairs;
-    const int tile = p.n_tiles - 1 - (int)(blockIdx.x / per_tile);
+    const int tile = (int)(blockIdx.x / per_tile);
     const int kvh = (int)(blockIdx.x % per_tile) / p.pairs, pair = (int)(blockIdx.x % per_tile) % p.pairs;
     const int rep = p.nq / p.nkv;
     const int head0 = kvh * rep + 2 * pair;

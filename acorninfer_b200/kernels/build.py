@@ -78,7 +78,13 @@ def _log(msg: str) -> None:
 
 
 def ensure_built(verbose: bool = True) -> Path:
-    """Returns the path of an up-to-date library, compiling what is stale."""
+    """Returns the path of an up-to-date library, compiling what is stale.  ``ACORN_KERNEL_LIB`` names
+    a library file to load as it is (a build with other compiler flags, for experiments)."""
+    given = os.environ.get("ACORN_KERNEL_LIB")
+    if given:
+        if not Path(given).is_file():
+            raise KernelBuildError(f"ACORN_KERNEL_LIB names {given}, which is not a file")
+        return Path(given)
     digest = _digest()
     for cand in (CSRC / "_build", build_dir()):
         stamp, lib = cand / "stamp.txt", cand / LIB_NAME

@@ -97,7 +97,8 @@ def bench_attn_prefill(a) -> None:
     tiles = torch.tensor([(0, q0) for q0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
     if a.kernel == "tc":
-        tiles = torch.tensor([(0, q0) for q0 in range(0, T, 128)], dtype=torch.int32, device=DEV)
+        # the kernel starts CTAs in list order: the tiles that read the most keys first
+        tiles = torch.tensor([(0, q0) for q0 in reversed(range(0, T, 128))], dtype=torch.int32, device=DEV)
         fn = lambda: ops.attention_prefill_tc(qkv, qkv.stride(0), k_pages, v_pages, table, base, row_start, row_pos,
                                               tiles, T, nq, nkv, d, d ** -0.5, None)
     else:

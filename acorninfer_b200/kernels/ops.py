@@ -509,7 +509,8 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, 
                          num_kv_heads: int, head_dim: int, scale: float, window: int | None,
                          out: torch.Tensor | None = None) -> torch.Tensor:
     """tcgen05/TMA prefill attention (bfloat16, head size 128) for the query tiles listed in
-    ``tiles`` (int32 [n, 2]: row, first token within the row; 128 tokens a tile at most)."""
+    ``tiles`` (int32 [n, 2]: row, first token within the row; 128 tokens a tile at most).  CTAs
+    start in the order of the list: give the tiles that read the most keys first."""
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc takes bfloat16")
     _check(k_pages, "k_pages", q.dtype, 4)
