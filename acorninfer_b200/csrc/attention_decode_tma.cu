@@ -10,8 +10,20 @@
 // reads them with the matching XOR.  Chunks start at multiples of 64 keys; keys outside
 // [lo, hi) are masked.  Rows of a last page beyond the request's length are read as they are
 // (the cache holds finite numbers) and get probability zero.
+//
+// Up to eight splits are merged inside this kernel: the CTAs of one (token, kv head) form a
+// thread-block cluster, every CTA sends its partial result of each query head (normalised output
+// and log-sum) into the shared memory of the CTA that finishes that head (head h by rank h mod
+// splits; remote stores through distributed shared memory), the cluster meets once, and the owners
+// write the merged rows.  No scratch in global memory and no merge kernel: one kernel and one
+// kernel boundary less in a decode layer.  More than eight splits (very few rows) go through
+// part_o / part_lse and attention_decode_merge_kernel as before.
+#include <cooperative_groups.h>
+
 #include "mma_helpers.cuh"
 #include "tcgen05_helpers.cuh"
+
+namespace cg = cooperative_groups;
 
 #define DT_D 128
 #define DT_CHUNK 64
@@ -35,7 +47,10 @@ struct DecodeTmaParams {
     float* part_lse;
     int table_stride, nq, nkv, logP, window, num_splits;
     float scale_log2;
+    int cluster_merge;       // 1: the splits of a (token, kv head) are a cluster and merge through shared memory
 };
+
+#define DT_RECV_ROW (DT_D + 4)              // floats a received partial row takes: the output, then its log-sum
 
 // byte offset of the 16-byte segment `seg` (0..15 over the 128 head dims) of key row `key` inside a
 // K or V stage region (two swizzled halves of [64][128 bytes])
@@ -59,6 +74,8 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // every CTA of the cluster says that it runs; nobody writes into a peer's shared memory before all have
+    if (p.cluster_merge) cg::this_cluster().barrier_arrive();
     pdl_wait();
     pdl_trigger();
 
@@ -72,7 +89,7 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     const int n_chunks = (hi - base_key + DT_CHUNK - 1) / DT_CHUNK;
     const int per = (n_chunks + p.num_splits - 1) / p.num_splits;
     const int c0 = split * per, c1 = min(n_chunks, c0 + per);
-    if (c0 >= c1) {
+    if (c0 >= c1 && !p.cluster_merge) {
         for (int h = threadIdx.x; h < rep; h += DT_THREADS)
             p.part_lse[((int64_t)ti * p.nq + kvh * rep + h) * p.num_splits + split] = -INFINITY;
         return;
@@ -224,25 +241,58 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
         }
     }
     __syncthreads();
+    // received partial rows: recv[rank of the sender][slot][DT_RECV_ROW], behind the ring and its barriers
+    float* recv = reinterpret_cast<float*>(bars + 2 * DT_STAGES + 2);
+    const int csize = p.cluster_merge ? p.num_splits : 1;
+    const int slots = (rep + csize - 1) / csize;
+    if (p.cluster_merge) cg::this_cluster().barrier_wait();
     for (int idx = threadIdx.x; idx < rep * DT_D; idx += DT_THREADS) {
         const int h = idx / DT_D, i = idx - h * DT_D;
         float mstar = -INFINITY;
+        if (c0 < c1) {
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mstar = fmaxf(mstar, sm_m[w * 16 + h]);
+            for (int w = 0; w < 4; ++w) mstar = fmaxf(mstar, sm_m[w * 16 + h]);
+        }
         float L = 0.f, acc = 0.f;
+        if (c0 < c1) {
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = exp2f(sm_m[w * 16 + h] - mstar);
-            L += sm_l[w * 16 + h] * f;
-            acc += sm_o[(w * 16 + h) * DT_D + i] * f;
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(sm_m[w * 16 + h] - mstar);
+                L += sm_l[w * 16 + h] * f;
+                acc += sm_o[(w * 16 + h) * DT_D + i] * f;
+            }
         }
         const int head = kvh * rep + h;
         if (p.num_splits == 1) {
             p.out[((int64_t)t * p.nq + head) * DT_D + i] = __float2bfloat16_rn(acc / L);
+        } else if (p.cluster_merge) {
+            // to the CTA that finishes this head; a split without keys sends a log-sum of -inf
+            const uint32_t dst = cluster_map(tc_smem(recv + ((split * slots + h / csize) * DT_RECV_ROW)), h % csize);
+            st_cluster_f32(dst + 4 * i, c0 < c1 ? acc / L : 0.f);
+            if (i == 0) st_cluster_f32(dst + 4 * DT_D, c0 < c1 ? mstar + log2f(L) : -INFINITY);
         } else {
             const int64_t slot = ((int64_t)ti * p.nq + head) * p.num_splits + split;
             p.part_o[slot * DT_D + i] = acc / L;
             if (i == 0) p.part_lse[slot] = mstar + log2f(L);
+        }
+    }
+    if (p.cluster_merge) {
+        cg::this_cluster().sync();                       // all partial rows have arrived
+        // the heads this CTA finishes: rank, rank + csize, ...; the splits in rank order
+        for (int idx = threadIdx.x; idx < slots * DT_D; idx += DT_THREADS) {
+            const int slot = idx / DT_D, i = idx - slot * DT_D;
+            const int h = split + slot * csize;
+            if (h >= rep) break;
+            float mstar = -INFINITY;
+            for (int q = 0; q < csize; ++q) mstar = fmaxf(mstar, recv[(q * slots + slot) * DT_RECV_ROW + DT_D]);
+            float L = 0.f, acc = 0.f;
+            for (int q = 0; q < csize; ++q) {
+                const float lse = recv[(q * slots + slot) * DT_RECV_ROW + DT_D];
+                const float f = lse == -INFINITY ? 0.f : exp2f(lse - mstar);
+                L += f;
+                acc += f * recv[(q * slots + slot) * DT_RECV_ROW + i];
+            }
+            p.out[((int64_t)t * p.nq + kvh * rep + h) * DT_D + i] = __float2bfloat16_rn(acc / L);
         }
     }
 }
@@ -261,28 +311,49 @@ extern "C" int acorn_attention_decode_tma_main(const void* q, int64_t q_stride, 
     if (n <= 0) return 0;
     if (!acorn_attention_decode_tma_supported(nq, nkv, d, P) || num_splits < 1 || num_splits > 32 || n > 65535)
         return ACORN_ERR_UNSUPPORTED;
-    if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return ACORN_ERR_UNSUPPORTED;
+    // two to eight splits without scratch: merged inside the kernel by a cluster
+    const int cluster_merge = num_splits > 1 && num_splits <= 8 && part_o == nullptr && part_lse == nullptr;
+    if (num_splits > 1 && !cluster_merge && (part_o == nullptr || part_lse == nullptr)) return ACORN_ERR_UNSUPPORTED;
     DecodeTmaParams p;
     p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.block_table = block_table;
     p.page_base = page_base; p.token_row = token_row; p.positions = positions; p.token_list = token_list;
     p.part_o = part_o; p.part_lse = part_lse; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
     p.logP = acorn_log2_exact_tc(P); p.window = window; p.num_splits = num_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.cluster_merge = cluster_merge;
     CUtensorMap mk, mv;
     const int box_rows = P < DT_CHUNK ? P : DT_CHUNK;
     int rc = make_map(&mk, k_pages, num_pages * nkv * P, d, d, 64, box_rows);
     if (rc) return rc;
     rc = make_map(&mv, v_pages, num_pages * nkv * P, d, d, 64, box_rows);
     if (rc) return rc;
-    const size_t smem = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16;
+    const int rep = nq / nkv;
+    const size_t recv = cluster_merge ? (size_t)num_splits * ((rep + num_splits - 1) / num_splits) * DT_RECV_ROW * sizeof(float) : 0;
+    const size_t smem = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16 + recv;
+    const size_t smem_max = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16 + (size_t)8 * 16 * DT_RECV_ROW * sizeof(float);
     static AcornPerDevice configured;
     if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+                                             (int)smem_max);
         if (e != cudaSuccess) return (int)e;
         configured.mark();
     }
-    return acorn_launch(attention_decode_tma_kernel, dim3(nkv, num_splits, n), dim3(DT_THREADS), smem, stream, mk, mv, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nkv, num_splits, n);
+    cfg.blockDim = dim3(DT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster_merge ? num_splits : 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = acorn_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel, mk, mv, p);
+    return e != cudaSuccess ? (int)e : acorn_launch_status();
 }
 
 extern "C" int acorn_attention_decode_tma_error() {

@@ -426,7 +426,8 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
     """Split-K decode attention (bfloat16) for single-token rows: the tokens 0..num_tokens-1, or
     those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
     not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
-    part_lse float32 [n, nq, splits]) is made here when absent and num_splits > 1."""
+    part_lse float32 [n, nq, splits]) is made here when absent and the kernel needs it (the TMA
+    kernel merges up to eight splits without; give ``scratch`` to force the separate merge pass)."""
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode takes bfloat16")
     if not attention_decode_supported(num_heads, num_kv_heads, head_dim):
@@ -439,25 +440,28 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
         raise KernelError(f"attention_decode: {n} tokens / {num_splits} splits beyond the grid limits")
     if out is None:
         out = torch.empty((num_tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    P = k_pages.shape[2]
+    if use_tma is None:
+        use_tma = bool(lib().acorn_attention_decode_tma_supported(num_heads, num_kv_heads, head_dim, P))
+    # the TMA kernel merges up to eight splits itself (a cluster, through shared memory): no scratch
+    in_kernel_merge = use_tma and 1 < num_splits <= 8 and scratch is None
     part_o = part_lse = None
-    if num_splits > 1:
+    if num_splits > 1 and not in_kernel_merge:
         if scratch is None:
             scratch = (torch.empty((n, num_heads, num_splits, head_dim), dtype=torch.float32, device=q.device),
                        torch.empty((n, num_heads, num_splits), dtype=torch.float32, device=q.device))
         part_o, part_lse = scratch
         if part_o.numel() < n * num_heads * num_splits * head_dim or part_lse.numel() < n * num_heads * num_splits:
             raise KernelError("attention_decode: scratch too small")
-    P = k_pages.shape[2]
-    if use_tma is None:
-        use_tma = bool(lib().acorn_attention_decode_tma_supported(num_heads, num_kv_heads, head_dim, P))
     if use_tma:
-        # head size 128: K/V tiles by TMA (attention_decode_tma.cu), then the common merge pass
+        # head size 128: K/V tiles by TMA (attention_decode_tma.cu); more than eight splits, or splits
+        # with scratch given, end in the common merge pass
         _ok(lib().acorn_attention_decode_tma_main(
             q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
             block_table.data_ptr(), page_base.data_ptr(), block_table.stride(0), token_row.data_ptr(),
             positions.data_ptr(), _ptr(token_list), n, num_heads, num_kv_heads, head_dim, P, float(scale),
             int(window or 0), num_splits, _ptr(part_o), _ptr(part_lse), _stream()), "attention_decode_tma")
-        if num_splits > 1:
+        if num_splits > 1 and not in_kernel_merge:
             _ok(lib().acorn_attention_decode_merge(part_o.data_ptr(), part_lse.data_ptr(), out.data_ptr(),
                                                    _ptr(token_list), n, num_heads, head_dim, num_splits, _stream()),
                 "attention_decode_merge")

@@ -154,7 +154,7 @@ BF16_TOL = dict(atol=2e-2, rtol=2e-2)
                                                (10, 2, 48, 16, None), (6, 3, 80, 8, 50), (16, 1, 64, 32, None),
                                                (5, 5, 112, 16, 129), (4, 2, 256, 16, None), (6, 2, 128, 8, 300),
                                                (8, 8, 128, 128, None), (4, 1, 128, 4, None)])
-@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("splits", [1, 3, 8, 32])
 def test_attention_decode_kernel(nq, nkv, d, P, window, splits):
     before = [0, 1, 63, 64, 65, 700, 127, 2000]           # one key; page and chunk edges; long rows
     qlens = [1] * len(before)
@@ -167,6 +167,18 @@ def test_attention_decode_kernel(nq, nkv, d, P, window, splits):
                                        lay["token_row"], lay["positions"], len(before), nq, nkv, d, d ** -0.5, window,
                                        splits, use_tma=False)
         assert torch.allclose(other.double().cpu(), want, **BF16_TOL)
+    if d == 128 and P >= 8:
+        # up to eight splits the TMA variant merged them inside the kernel (a cluster); with scratch given
+        # it takes the separate merge pass, which must agree
+        n = len(before)
+        scratch = (torch.empty((n, nq, splits, d), dtype=torch.float32, device=DEV),
+                   torch.empty((n, nq, splits), dtype=torch.float32, device=DEV))
+        counts = dict(ops().COUNTS)
+        passes = ops().attention_decode(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
+                                        lay["token_row"], lay["positions"], n, nq, nkv, d, d ** -0.5, window, splits,
+                                        scratch=scratch)
+        assert torch.allclose(passes.double().cpu(), want, **BF16_TOL)
+        assert ops().COUNTS.get("attention_decode_merge", 0) - counts.get("attention_decode_merge", 0) == (splits > 1)
         assert ops().attention_decode_tma_error() == 0
     # a second run gives the same bits
     again = ops().attention_decode(wide, wide.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],

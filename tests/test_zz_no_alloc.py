@@ -63,8 +63,11 @@ def dense_float64(lay, qkv, k_pages, v_pages, before, nq, nkv, d, P):
 def run_both(lib, lay, qkv, k_pages, v_pages, nq, nkv, d, splits):
     from acorninfer_b200.kernels import ops
     n = qkv.shape[0]
+    # the ordinary entry point of the same kernel (scratch from the caller; head size 128 would
+    # otherwise take the TMA variant, which merges its splits differently)
     want = ops.attention_decode(qkv, qkv.stride(0), k_pages, v_pages, lay["block_table"], lay["page_base"],
-                                lay["token_row"], lay["positions"], n, nq, nkv, d, d ** -0.5, None, splits)
+                                lay["token_row"], lay["positions"], n, nq, nkv, d, d ** -0.5, None, splits,
+                                use_tma=False)
     got = torch.zeros_like(want)
     rc = lib.acorn_attention_decode_noalloc(
         qkv.data_ptr(), qkv.stride(0), got.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
