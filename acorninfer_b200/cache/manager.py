@@ -52,6 +52,17 @@ class RequestCache:
     tables: list[list[int]] = field(default_factory=list)   # per group: physical page ids
     page_base: list[int] = field(default_factory=list)      # per group: logical index of tables[g][0]
     closed: bool = False
+    _arrays: dict = field(default_factory=dict, repr=False)  # per group: tables[g] as an int32 array, while unchanged
+
+    def table_array(self, group: int):
+        """``tables[group]`` as a numpy int32 array, rebuilt only after the table changed (a page is
+        added every ``page_size`` tokens, so most steps reuse it)."""
+        arr = self._arrays.get(group)
+        if arr is None or arr.size != len(self.tables[group]):
+            import numpy as np
+            arr = np.asarray(self.tables[group], dtype=np.int32)
+            self._arrays[group] = arr
+        return arr
 
 
 class CacheManager:
@@ -135,11 +146,10 @@ class CacheManager:
 
     def pages_needed(self, rc: RequestCache | None, new_length: int) -> list[int]:
         """Per group, the pages to add so that a step can bring the request to ``new_length``."""
-        out = []
-        for g in self.groups:
-            have_to = (rc.page_base[g.index] + len(rc.tables[g.index])) if rc is not None else 0
-            out.append(max(0, ceil_div(new_length, self.page_size) - have_to))
-        return out
+        want = -(-new_length // self.page_size)
+        if rc is None:
+            return [want] * len(self.groups)
+        return [max(0, want - b - len(t)) for b, t in zip(rc.page_base, rc.tables)]
 
     def peak_pages(self, total_length: int, max_portion: int | None) -> list[int]:
         """Per group, the most pages a request of ``total_length`` tokens holds at once when it is
@@ -170,13 +180,17 @@ class CacheManager:
         if new_length < rc.length:
             raise ValueError(f"cannot extend request {rc.request_id!r} from {rc.length} to {new_length}")
         need = self.pages_needed(rc, new_length)
+        if not any(need):
+            return
         for g, n in zip(self.groups, need):
             if n > g.pool.num_free:
                 raise PoolExhausted(
                     f"request {rc.request_id!r}: group {g.index} needs {n} page(s) for length {new_length}, "
                     f"{g.pool.num_free} free of {g.pool.total}")
         for g, n in zip(self.groups, need):
-            rc.tables[g.index].extend(g.pool.allocate(n))
+            if n:
+                rc.tables[g.index].extend(g.pool.allocate(n))
+                rc._arrays.pop(g.index, None)
 
     def trim(self, rc: RequestCache) -> None:
         """Gives back the pages taken by ``extend`` beyond the committed length: for a step that
@@ -188,6 +202,7 @@ class CacheManager:
             if len(table) > keep:
                 g.pool.free(table[keep:])
                 del table[keep:]
+                rc._arrays.pop(g.index, None)
 
     def commit(self, rc: RequestCache, new_length: int) -> None:
         """Records that the step wrote up to ``new_length``; windowed groups give back the pages
@@ -207,6 +222,7 @@ class CacheManager:
                 g.pool.free(table[:drop])
                 del table[:drop]
                 rc.page_base[g.index] += drop
+                rc._arrays.pop(g.index, None)
 
     def close(self, rc: RequestCache) -> None:
         if rc.closed:
@@ -214,6 +230,7 @@ class CacheManager:
         for g in self.groups:
             g.pool.free(rc.tables[g.index])
             rc.tables[g.index] = []
+        rc._arrays.clear()
         self.slots.free([rc.slot])
         rc.closed = True
         rc.length = 0

@@ -127,40 +127,37 @@ def plan_step(entries: list[StepEntry], manager: CacheManager, builders: dict | 
     R = len(entries)
     lens = [len(e.tokens) for e in entries]
     T = sum(lens)
-    token_ids = np.empty(T, np.int32)
-    positions = np.empty(T, np.int32)
-    token_row = np.empty(T, np.int32)
-    row_start = np.zeros(R + 1, np.int32)
-    row_pos = np.empty(R, np.int32)
-    row_slot = np.empty(R, np.int32)
-    logit_tokens: list[int] = []
-    off = 0
-    for r, e in enumerate(entries):
-        n = lens[r]
-        token_ids[off:off + n] = e.tokens
-        positions[off:off + n] = np.arange(e.cache.length, e.cache.length + n, dtype=np.int32)
-        token_row[off:off + n] = r
-        row_pos[r] = e.cache.length
-        row_slot[r] = e.cache.slot
-        logit_tokens.extend(off + int(w) for w in e.want)
-        off += n
-        row_start[r + 1] = off
+    i32 = np.int32
+    starts = [e.cache.length for e in entries]
+    row_pos = np.asarray(starts, i32)
+    row_slot = np.asarray([e.cache.slot for e in entries], i32)
+    lens_a = np.asarray(lens, i32)
+    row_start = np.zeros(R + 1, i32)
+    np.cumsum(lens_a, out=row_start[1:])
+    token_row = np.repeat(np.arange(R, dtype=i32), lens_a)
+    # position of a token = tokens of its request before the step + its index within the row
+    positions = (np.arange(T, dtype=i32) - row_start[token_row] + row_pos[token_row]).astype(i32, copy=False)
+    if T == R:
+        token_ids = np.asarray([e.tokens[0] for e in entries], i32)
+    else:
+        flat: list[int] = []
+        for e in entries:
+            flat.extend(e.tokens)
+        token_ids = np.asarray(flat, i32)
+    logit_tokens = [int(row_start[r]) + int(w) for r, e in enumerate(entries) for w in e.want]
     groups = []
     P = manager.page_size
     for g in manager.groups:
-        tables = [e.cache.tables[g.index] for e in entries]
-        stride = _table_stride(max((len(t) for t in tables), default=0))
-        bt = np.zeros((R, stride), np.int32)
-        kv_len = np.empty(R, np.int32)
-        base = np.empty(R, np.int32)
+        gi = g.index
+        stride = _table_stride(max((len(e.cache.tables[gi]) for e in entries), default=0))
+        bt = np.zeros((R, stride), i32)
+        base = np.asarray([e.cache.page_base[gi] for e in entries], i32)
+        kv_len = row_pos + lens_a
         for r, e in enumerate(entries):
-            t = tables[r]
-            new_len = e.cache.length + lens[r]
-            if (e.cache.page_base[g.index] + len(t)) * P < new_len:
-                raise BatchError(f"request {e.cache.request_id!r}: pages of group {g.index} do not cover length {new_len}")
-            bt[r, :len(t)] = t
-            kv_len[r] = new_len
-            base[r] = e.cache.page_base[g.index]
+            t = e.cache.table_array(gi)
+            if (int(base[r]) + t.size) * P < int(kv_len[r]):
+                raise BatchError(f"request {e.cache.request_id!r}: pages of group {gi} do not cover length {int(kv_len[r])}")
+            bt[r, :t.size] = t
         groups.append(GroupPlan(kv_len, base, bt, int(kv_len.max()) if R else 0))
     patch = [(int(row_start[r]), e.from_device) for r, e in enumerate(entries) if e.from_device is not None]
     plan = StepPlan(T, R, token_ids, positions, token_row, row_start, row_pos, row_slot,

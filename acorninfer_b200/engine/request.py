@@ -21,7 +21,7 @@ class RequestStatus(enum.Enum):
     FINISHED = "finished"
 
 
-@dataclass
+@dataclass(eq=False)          # requests are compared by identity (field-wise equality would walk the token lists)
 class Request:
     seq_id: int
     prompt_ids: list[int]

@@ -84,23 +84,25 @@ class Scheduler:
         need = [0] * len(self.manager.groups)
         # a request whose last allowed token is sampled (perhaps not yet read by the host) runs no more
         active = [r for r in self.running if not r.exhausted and not r.is_finished]
-        decoders = [r for r in active if r.cursor == r.num_tokens - 1 and r.num_generated]
-        for r in decoders:
-            # Decoded tokens are never starved by the budget: every running request past its
-            # prompt advances each step (reference: decodes are outside the budget).
-            portions.append(Portion(r, r.cursor, 1, True))
-            budget -= 1
+        prompts = []
         for r in active:
-            if r in decoders:
-                continue
+            if r.cursor == r.num_tokens - 1 and r.num_generated:
+                # Decoded tokens are never starved by the budget: every running request past its
+                # prompt advances each step (reference: decodes are outside the budget).
+                portions.append(Portion(r, r.cursor, 1, True))
+                budget -= 1
+            else:
+                prompts.append(r)
+        for r in prompts:
             remaining = r.num_tokens - r.cursor
             length = min(remaining, max(budget, 0))
             if length <= 0:
                 continue
             budget -= length
             portions.append(Portion(r, r.cursor, length, r.cursor + length == r.num_tokens))
+        pages_needed = self.manager.pages_needed
         for p in portions:
-            for gi, n in enumerate(self.manager.pages_needed(p.request.cache, p.start + p.length)):
+            for gi, n in enumerate(pages_needed(p.request.cache, p.start + p.length)):
                 need[gi] += n
         return portions, need, budget
 

@@ -63,7 +63,8 @@ sm_count = ops.device_sms
 _CTA_GBS, _HBM_GBS, _WAVE_US, _MERGE_US = 35.0, 6500.0, 2.0, 3.0
 
 
-def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, num_sms: int = B200_SMS) -> int:
+def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, num_sms: int = B200_SMS,
+                  merge_free_upto: int = 1) -> int:
     """Splits of the key range.  ``key_bound`` bounds the keys any row reads; it changes only with
     the table stride, so a captured step keeps its grid.
 
@@ -72,7 +73,8 @@ def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, n
     splits (more CTAs in flight); a count just above a multiple of 296 wants splits too (a last
     wave of few long CTAs takes as long as one CTA takes alone: 40 rows of 8 kv heads, unsplit,
     take 149 us against 123 us in three splits); a count that fills its last wave well wants
-    none.  The splits with the least estimated time are taken."""
+    none.  The splits with the least estimated time are taken.  ``merge_free_upto``: up to this many
+    splits cost no merge pass (the TMA kernel merges up to eight inside itself)."""
     _TARGET_CTAS = 2 * num_sms
     pairs = max(1, rows * num_kv_heads)
     most = max(1, min(-(-key_bound // _CHUNK), 32))
@@ -85,11 +87,22 @@ def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, n
         us = full * (max(alone_us, _TARGET_CTAS * kb / _HBM_GBS) + _WAVE_US)
         if rest:
             us += max(alone_us, rest * kb / _HBM_GBS) + _WAVE_US
-        if s > 1:
+        if s > merge_free_upto:
             us += _MERGE_US
         if best_us is None or us <= best_us + 1e-9:                  # equal estimates: more CTAs in flight
             best, best_us = s, us
     return best
+
+
+_MERGE_FREE: dict = {}
+
+
+def _merge_free(nq: int, nkv: int, d: int, P: int) -> int:
+    """Splits that the decode kernel for these sizes merges itself (1: none)."""
+    key = (nq, nkv, d, P)
+    if key not in _MERGE_FREE:
+        _MERGE_FREE[key] = 8 if ops.lib().acorn_attention_decode_tma_supported(nq, nkv, d, P) else 1
+    return _MERGE_FREE[key]
 
 
 def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, d: int, scale: float,
@@ -101,7 +114,7 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
             bound = group.block_table.shape[1] * P
             if window:
                 bound = min(bound, window)
-            splits = decode_splits(inputs.num_rows, nkv, bound, d, sm_count(qkv.device))
+            splits = decode_splits(inputs.num_rows, nkv, bound, d, sm_count(qkv.device), _merge_free(nq, nkv, d, P))
             return ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                         group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
                                         nq, nkv, d, scale, window, splits)
@@ -133,7 +146,7 @@ def paged_attention(qkv: torch.Tensor, inputs, group, cache, nq: int, nkv: int, 
                 ops.attention_decode(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
                                      group.page_base, inputs.token_row, inputs.positions, inputs.num_tokens,
                                      nq, nkv, d, scale, window,
-                                     decode_splits(n_single, nkv, bound, d, sm_count(qkv.device)),
+                                     decode_splits(n_single, nkv, bound, d, sm_count(qkv.device), _merge_free(nq, nkv, d, P)),
                                      token_list=x["attention.single_tokens"], out=out)
             return out
     return ops.attention_plain(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, group.block_table,
