@@ -76,8 +76,10 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     __syncthreads();
     // every CTA of the cluster says that it runs; nobody writes into a peer's shared memory before all have
     if (p.cluster_merge) cg::this_cluster().barrier_arrive();
-    pdl_wait();
-    pdl_trigger();
+    // What follows up to pdl_wait() reads only the step's own arrays (token list, rows, positions,
+    // block tables: written by the host before the step), not what the kernel before this one
+    // produces (the queries and the newest keys and values): the chain of dependent lookups that
+    // ends in the first cache rows runs while that kernel finishes.
 
     const int kvh = blockIdx.x, split = blockIdx.y, ti = blockIdx.z;
     const int t = p.token_list ? p.token_list[ti] : ti;
@@ -90,6 +92,8 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     const int per = (n_chunks + p.num_splits - 1) / p.num_splits;
     const int c0 = split * per, c1 = min(n_chunks, c0 + per);
     if (c0 >= c1 && !p.cluster_merge) {
+        pdl_wait();
+        pdl_trigger();
         for (int h = threadIdx.x; h < rep; h += DT_THREADS)
             p.part_lse[((int64_t)ti * p.nq + kvh * rep + h) * p.num_splits + split] = -INFINITY;
         return;
@@ -118,6 +122,8 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
             return ((page * p.nkv + kvh) << p.logP) + (key & (P - 1));
         };
         int rows_next = row_of(lane);
+        pdl_wait();
+        pdl_trigger();
         bool good = true;
         for (int b0 = 0; b0 < n_ops && good; b0 += 32) {
             const int rows_cur = rows_next;
@@ -144,6 +150,8 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
         }
     } else {
         // ---------------------------------------------------------------- compute warps
+        pdl_wait();
+        pdl_trigger();
         uint32_t qa[DT_D / 16][4];
         {
             const bf16* qrow = p.q + (int64_t)t * p.q_stride + (int64_t)kvh * rep * DT_D;
