@@ -11,13 +11,15 @@
 // [lo, hi) are masked.  Rows of a last page beyond the request's length are read as they are
 // (the cache holds finite numbers) and get probability zero.
 //
-// Up to eight splits are merged inside this kernel: the CTAs of one (token, kv head) form a
+// Up to sixteen splits are merged inside this kernel: the CTAs of one (token, kv head) form a
 // thread-block cluster, every CTA sends its partial result of each query head (normalised output
 // and log-sum) into the shared memory of the CTA that finishes that head (head h by rank h mod
 // splits; remote stores through distributed shared memory), the cluster meets once, and the owners
 // write the merged rows.  No scratch in global memory and no merge kernel: one kernel and one
-// kernel boundary less in a decode layer.  More than eight splits (very few rows) go through
-// part_o / part_lse and attention_decode_merge_kernel as before.
+// kernel boundary less in a decode layer.  Clusters of more than eight CTAs are the non-portable
+// size the B200 allows (asked for with cudaFuncAttributeNonPortableClusterSizeAllowed).  More than
+// sixteen splits (very few rows at a long context), or received rows beyond DT_RECV_MAX_BYTES, go
+// through part_o / part_lse and attention_decode_merge_kernel as before.
 #include <cooperative_groups.h>
 
 #include "mma_helpers.cuh"
@@ -51,6 +53,8 @@ struct DecodeTmaParams {
 };
 
 #define DT_RECV_ROW (DT_D + 4)              // floats a received partial row takes: the output, then its log-sum
+#define DT_CLUSTER_MAX 16
+#define DT_RECV_MAX_BYTES (32 * 1024)
 
 // byte offset of the 16-byte segment `seg` (0..15 over the 128 head dims) of key row `key` inside a
 // K or V stage region (two swizzled halves of [64][128 bytes])
@@ -305,6 +309,16 @@ __global__ void __launch_bounds__(DT_THREADS) attention_decode_tma_kernel(const 
     }
 }
 
+// Splits up to which a call with these sizes and no scratch merges inside the kernel (1: none).
+extern "C" int acorn_attention_decode_tma_merges(int nq, int nkv) {
+    if (nkv <= 0 || nq % nkv) return 1;
+    const int rep = nq / nkv;
+    int best = 1;
+    for (int s = 2; s <= DT_CLUSTER_MAX; ++s)
+        if ((size_t)s * ((rep + s - 1) / s) * DT_RECV_ROW * sizeof(float) <= DT_RECV_MAX_BYTES) best = s;
+    return best;
+}
+
 extern "C" int acorn_attention_decode_tma_supported(int nq, int nkv, int d, int P) {
     return nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && d == DT_D && P >= 8 && (P & (P - 1)) == 0;
 }
@@ -319,8 +333,11 @@ extern "C" int acorn_attention_decode_tma_main(const void* q, int64_t q_stride, 
     if (n <= 0) return 0;
     if (!acorn_attention_decode_tma_supported(nq, nkv, d, P) || num_splits < 1 || num_splits > 32 || n > 65535)
         return ACORN_ERR_UNSUPPORTED;
-    // two to eight splits without scratch: merged inside the kernel by a cluster
-    const int cluster_merge = num_splits > 1 && num_splits <= 8 && part_o == nullptr && part_lse == nullptr;
+    // two to sixteen splits without scratch: merged inside the kernel by a cluster
+    const int rep = nq / nkv;
+    const size_t recv_need = (size_t)num_splits * ((rep + num_splits - 1) / num_splits) * DT_RECV_ROW * sizeof(float);
+    const int cluster_merge = num_splits > 1 && num_splits <= DT_CLUSTER_MAX && recv_need <= DT_RECV_MAX_BYTES &&
+                              part_o == nullptr && part_lse == nullptr;
     if (num_splits > 1 && !cluster_merge && (part_o == nullptr || part_lse == nullptr)) return ACORN_ERR_UNSUPPORTED;
     DecodeTmaParams p;
     p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.block_table = block_table;
@@ -335,14 +352,15 @@ extern "C" int acorn_attention_decode_tma_main(const void* q, int64_t q_stride, 
     if (rc) return rc;
     rc = make_map(&mv, v_pages, num_pages * nkv * P, d, d, 64, box_rows);
     if (rc) return rc;
-    const int rep = nq / nkv;
-    const size_t recv = cluster_merge ? (size_t)num_splits * ((rep + num_splits - 1) / num_splits) * DT_RECV_ROW * sizeof(float) : 0;
+    const size_t recv = cluster_merge ? recv_need : 0;
     const size_t smem = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16 + recv;
-    const size_t smem_max = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16 + (size_t)8 * 16 * DT_RECV_ROW * sizeof(float);
+    const size_t smem_max = (size_t)DT_STAGES * DT_STAGE_BYTES + 2 * DT_STAGES * 8 + 16 + DT_RECV_MAX_BYTES;
     static AcornPerDevice configured;
     if (!configured.seen()) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem_max);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return (int)e;
         configured.mark();
     }

@@ -63,6 +63,13 @@ sm_count = ops.device_sms
 _CTA_GBS, _HBM_GBS, _WAVE_US, _MERGE_US = 35.0, 6500.0, 2.0, 3.0
 
 
+def merged_in_kernel(splits: int, limit: int) -> bool:
+    """Whether a decode kernel that merges up to ``limit`` splits inside itself (a cluster) does so for
+    this many: clusters of up to 8 CTAs, and of 16; sizes between (9 splits took 24 us where the
+    separate merge pass took 17) are left to the merge pass."""
+    return splits <= min(limit, 8) or (splits == 16 and limit >= 16)
+
+
 def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, num_sms: int = B200_SMS,
                   merge_free_upto: int = 1) -> int:
     """Splits of the key range.  ``key_bound`` bounds the keys any row reads; it changes only with
@@ -74,7 +81,7 @@ def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, n
     wave of few long CTAs takes as long as one CTA takes alone: 40 rows of 8 kv heads, unsplit,
     take 149 us against 123 us in three splits); a count that fills its last wave well wants
     none.  The splits with the least estimated time are taken.  ``merge_free_upto``: up to this many
-    splits cost no merge pass (the TMA kernel merges up to eight inside itself)."""
+    splits cost no merge pass (the TMA kernel merges up to sixteen inside itself)."""
     _TARGET_CTAS = 2 * num_sms
     pairs = max(1, rows * num_kv_heads)
     most = max(1, min(-(-key_bound // _CHUNK), 32))
@@ -87,7 +94,7 @@ def decode_splits(rows: int, num_kv_heads: int, key_bound: int, head_dim: int, n
         us = full * (max(alone_us, _TARGET_CTAS * kb / _HBM_GBS) + _WAVE_US)
         if rest:
             us += max(alone_us, rest * kb / _HBM_GBS) + _WAVE_US
-        if s > merge_free_upto:
+        if not merged_in_kernel(s, merge_free_upto):
             us += _MERGE_US
         if best_us is None or us <= best_us + 1e-9:                  # equal estimates: more CTAs in flight
             best, best_us = s, us
@@ -101,7 +108,8 @@ def _merge_free(nq: int, nkv: int, d: int, P: int) -> int:
     """Splits that the decode kernel for these sizes merges itself (1: none)."""
     key = (nq, nkv, d, P)
     if key not in _MERGE_FREE:
-        _MERGE_FREE[key] = 8 if ops.lib().acorn_attention_decode_tma_supported(nq, nkv, d, P) else 1
+        _MERGE_FREE[key] = (ops.lib().acorn_attention_decode_tma_merges(nq, nkv)
+                            if ops.lib().acorn_attention_decode_tma_supported(nq, nkv, d, P) else 1)
     return _MERGE_FREE[key]
 
 

@@ -106,6 +106,7 @@ class _Sigs:
                                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                        c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]
     acorn_attention_decode_tma_supported = [c_int, c_int, c_int, c_int]
+    acorn_attention_decode_tma_merges = [c_int, c_int]
     acorn_attention_decode_tma_error = []
     acorn_attention_decode_merge = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     acorn_attention_prefill = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -232,7 +233,7 @@ class _TimedLib:
 
     def __getattr__(self, name):
         fn = getattr(self._library, name)
-        if not name.startswith("acorn_") or name.endswith(("_supported", "_error")):
+        if not name.startswith("acorn_") or name.endswith(("_supported", "_error", "_merges")):
             return fn
 
         def timed(*args):
@@ -427,7 +428,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
     those listed in ``token_list``.  ``out`` is [all tokens of the step, nq * d]; rows of tokens
     not handled are left as they are.  ``scratch`` = (part_o float32 [n, nq, splits, d],
     part_lse float32 [n, nq, splits]) is made here when absent and the kernel needs it (the TMA
-    kernel merges up to eight splits without; give ``scratch`` to force the separate merge pass)."""
+    kernel merges up to sixteen splits without; give ``scratch`` to force the separate merge pass)."""
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode takes bfloat16")
     if not attention_decode_supported(num_heads, num_kv_heads, head_dim):
@@ -443,8 +444,9 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
     P = k_pages.shape[2]
     if use_tma is None:
         use_tma = bool(lib().acorn_attention_decode_tma_supported(num_heads, num_kv_heads, head_dim, P))
-    # the TMA kernel merges up to eight splits itself (a cluster, through shared memory): no scratch
-    in_kernel_merge = use_tma and 1 < num_splits <= 8 and scratch is None
+    # the TMA kernel merges up to sixteen splits itself (a cluster, through shared memory): no scratch
+    limit = lib().acorn_attention_decode_tma_merges(num_heads, num_kv_heads) if use_tma and scratch is None else 1
+    in_kernel_merge = num_splits > 1 and (num_splits <= min(limit, 8) or (num_splits == 16 and limit >= 16))
     part_o = part_lse = None
     if num_splits > 1 and not in_kernel_merge:
         if scratch is None:
@@ -454,7 +456,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pa
         if part_o.numel() < n * num_heads * num_splits * head_dim or part_lse.numel() < n * num_heads * num_splits:
             raise KernelError("attention_decode: scratch too small")
     if use_tma:
-        # head size 128: K/V tiles by TMA (attention_decode_tma.cu); more than eight splits, or splits
+        # head size 128: K/V tiles by TMA (attention_decode_tma.cu); more than sixteen splits, or splits
         # with scratch given, end in the common merge pass
         _ok(lib().acorn_attention_decode_tma_main(
             q.data_ptr(), q_stride, out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],

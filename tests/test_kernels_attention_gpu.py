@@ -154,7 +154,7 @@ BF16_TOL = dict(atol=2e-2, rtol=2e-2)
                                                (10, 2, 48, 16, None), (6, 3, 80, 8, 50), (16, 1, 64, 32, None),
                                                (5, 5, 112, 16, 129), (4, 2, 256, 16, None), (6, 2, 128, 8, 300),
                                                (8, 8, 128, 128, None), (4, 1, 128, 4, None)])
-@pytest.mark.parametrize("splits", [1, 3, 8, 32])
+@pytest.mark.parametrize("splits", [1, 3, 8, 16, 32])
 def test_attention_decode_kernel(nq, nkv, d, P, window, splits):
     before = [0, 1, 63, 64, 65, 700, 127, 2000]           # one key; page and chunk edges; long rows
     qlens = [1] * len(before)
@@ -168,7 +168,7 @@ def test_attention_decode_kernel(nq, nkv, d, P, window, splits):
                                        splits, use_tma=False)
         assert torch.allclose(other.double().cpu(), want, **BF16_TOL)
     if d == 128 and P >= 8:
-        # up to eight splits the TMA variant merged them inside the kernel (a cluster); with scratch given
+        # up to sixteen splits the TMA variant merged them inside the kernel (a cluster); with scratch given
         # it takes the separate merge pass, which must agree
         n = len(before)
         scratch = (torch.empty((n, nq, splits, d), dtype=torch.float32, device=DEV),
