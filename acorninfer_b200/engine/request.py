@@ -1,6 +1,10 @@
 """A request inside the engine: its tokens, its sampling parameters, where it stands.
 
-Reference: ``Sequence`` / ``RequestStatus`` in ``acorninfer/engine/sequence.py:12-46``.
+Reference: ``Sequence`` / ``RequestStatus`` in ``acorninfer/engine/sequence.py:12-46``.  The
+three status values and the fields ``seq_id .. last_token_at`` with ``num_tokens``, ``all_ids`` and
+``is_finished`` are the reference's interface, kept name for name because its callers (the
+benchmark protocol's ``engine.seqs[i]``, the time stamps) read them; ``cursor``, ``pending``,
+``exhausted``, ``tokens()``, ``preemptions`` and ``cache`` are this engine's.
 ``cursor`` counts the tokens of ``all_ids`` whose keys and values are in the cache; a
 request whose pages were taken away (preemption) starts again from cursor 0 over
 ``all_ids`` (prompt plus what it has generated), which recomputes the same cache.
