@@ -171,7 +171,10 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
         for (int k = 0; k < 4; ++k) {
             const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
             const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
-            __nv_bfloat162 o = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+            // exp and the quotient by the fast float32 instructions (relative error about 2^-22, far below
+            // the bfloat16 rounding of the result): with the exact ones the kernel is bound by arithmetic
+            __nv_bfloat162 o = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x,
+                                                     __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
             ow[k] = *reinterpret_cast<uint32_t*>(&o);
         }
         return make_uint4(ow[0], ow[1], ow[2], ow[3]);
