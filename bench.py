@@ -233,6 +233,37 @@ def _mean_by_tag(records) -> dict:
     return {k: (n, total / n) for k, (n, total) in acc.items()}
 
 
+def _in_step_contributions(runner, step, order: list, torch) -> dict:
+    """Per (entry point, tag): the mean of what its launches add to the end time of a captured, replayed
+    step (kernels overlap under programmatic dependent launch, so durations would count time twice),
+    from the profiler's kernel records.  ``order`` is the step's launch list from an eager run, which the
+    records must match in number; {} when they do not or the profiler is not to be had."""
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        for _ in range(4):              # seen, captured, replayed
+            step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "emcpy" not in e.name
+               and "emset" not in e.name]
+        evs.sort(key=lambda e: e.time_range.start)
+        if len(evs) != len(order):
+            return {}
+        ends = sorted(range(len(evs)), key=lambda i: evs[i].time_range.end)
+        prev = evs[0].time_range.start
+        acc: dict = {}
+        for i in ends:
+            e = acc.setdefault(order[i], [0, 0.0])
+            e[0] += 1
+            e[1] += evs[i].time_range.end - prev
+            prev = evs[i].time_range.end
+        return {k: total / n for k, (n, total) in acc.items()}
+    except Exception:
+        return {}
+
+
 def kernel_table(runner, nums: dict, conf: dict, B: int, ctx: int, T: int, pk: dict, torch) -> dict:
     """Every launch of one decode step (batch B at context ctx) and of one prefill step (T tokens),
     each timed alone with CUDA events in an eager step; the products, attention and the output
@@ -258,7 +289,12 @@ def kernel_table(runner, nums: dict, conf: dict, B: int, ctx: int, T: int, pk: d
         run_ahead()
         with ops.kernel_timer() as timer:
             step()
-        dec = _mean_by_tag(timer.records())
+        records = timer.records()
+        dec = _mean_by_tag(records)
+        # the same step captured and replayed, under the profiler: what each kernel adds to the step's end
+        runner.decode_graph = graphs
+        in_step = _in_step_contributions(runner, step, [(w, t) for w, t, _ in records], torch) if graphs else {}
+        runner.decode_graph = False
         for rc in reqs:
             runner.close(rc)
         rc = runner.open("ktp")
@@ -277,7 +313,11 @@ def kernel_table(runner, nums: dict, conf: dict, B: int, ctx: int, T: int, pk: d
         if us is None:
             return {"us": None}
         gbs = nbytes / us / 1e3
-        return {"us": round(us, 2), "calls": n, "MB": round(nbytes / 1e6, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / hbm, 3)}
+        out = {"us": round(us, 2), "calls": n, "MB": round(nbytes / 1e6, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / hbm, 3)}
+        if key in in_step:
+            out["in_step_us"] = round(in_step[key], 2)
+            out["in_step_frac_hbm"] = round(nbytes / in_step[key] / 1e3 / hbm, 3)
+        return out
 
     def flop(key, flops):
         n, us = pre.get(key, (0, None))
@@ -297,6 +337,8 @@ def kernel_table(runner, nums: dict, conf: dict, B: int, ctx: int, T: int, pk: d
         "lm_head": mem(("gemm_tc", f"{B}x{V}x{H}"), 2 * V * H),
         "sum_us_layer": round(sum(us for (what, tag), (n, us) in dec.items()
                                   if what.startswith(("gemm_tc", "attention")) and not tag.startswith(f"{B}x{V}x")), 1),
+        "in_step_us_layer": round(sum(us for (what, tag), us in in_step.items()
+                                      if what.startswith(("gemm_tc", "attention")) and not tag.startswith(f"{B}x{V}x")), 1),
     }
     prefill = {
         "attention_prefill": flop(("attention_prefill_tc", ""), nq * d * 4.0 * (T * (T + 1) / 2)),
@@ -307,8 +349,9 @@ def kernel_table(runner, nums: dict, conf: dict, B: int, ctx: int, T: int, pk: d
         "other_own_kernels_us": round(sum(us for (what, tag), (n, us) in pre.items()
                                           if what in ("add_rmsnorm", "swiglu", "qk_rope_kv")), 1),
     }
-    return {"timing": "CUDA events around each launch of one eager step queued behind a busy device: each kernel alone "
-                      "(in the captured step they overlap through programmatic dependent launch), mean over the layers",
+    return {"timing": "us: CUDA events around each launch of one eager step queued behind a busy device, each kernel alone; "
+                      "in_step_us: what a launch adds to the end time of the captured, replayed step (profiler records; "
+                      "kernels overlap through programmatic dependent launch); means over the layers",
             f"decode_b{B}_ctx{ctx}": decode, f"prefill_{T}": prefill}
 
 
