@@ -58,6 +58,27 @@ def test_add_rmsnorm(dtype, H):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,H", [(1024, 4096), (1500, 1000), (2500, 132), (1100, 8200)])
+def test_add_rmsnorm_many_rows(dtype, rows, H):
+    """Thousands of rows (a prompt portion): more blocks than fit on the device at once, widths that do
+    not fill the last vector step and one beyond what the vector kernel keeps in registers, with and
+    without the residual sum."""
+    eps = 1e-5
+    resid = torch.randn(rows, H, device=DEV)
+    delta = torch.randn(rows, H, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, device=DEV)
+    r = resid.clone()
+    out = ops().add_rmsnorm(r, delta, w, eps, dtype)
+    want_resid = resid + delta.float()
+    assert torch.allclose(r, want_resid, atol=1e-6)
+    assert torch.allclose(out.double(), plain.rms_norm(want_resid.double(), w.double(), eps), **tol(dtype))
+    r2 = resid.clone()
+    out2 = ops().add_rmsnorm(r2, None, w, eps, dtype)
+    assert torch.equal(r2, resid)
+    assert torch.allclose(out2.double(), plain.rms_norm(resid.double(), w.double(), eps), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu_and_cast(dtype):
     gu = torch.randn(9, 2 * 200, device=DEV).to(dtype)
     out = ops().swiglu(gu)
