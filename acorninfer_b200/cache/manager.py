@@ -42,9 +42,9 @@ class CacheGroup:
         return self.needs.window
 
 
-@dataclass
+@dataclass(eq=False)
 class RequestCache:
-    """What one live request holds."""
+    """What one live request holds (compared by identity)."""
 
     request_id: object
     slot: int
