@@ -10,8 +10,10 @@ cluster at K = 12,288, the output matrix at N = 151,936, TMA decode attention wi
 launch plan picks, tcgen05 prefill attention continuing inside a 128-key block, and above 32 rows
 the library products with the stand-alone norm / rotation / SwiGLU kernels.
 
-Tolerances are measured (logits have magnitude about 4): float32 differs from the float64 plain
-result by up to 4e-6; bfloat16 by up to 5e-2.
+Tolerances are measured (logits have a standard deviation of 1.3 and reach 6): the float32 engine
+differs from the float64 plain result by up to 3.7e-5 (sums over 12,288 terms; relative
+root-mean-square 5.5e-6), the bfloat16 engine by up to 7.5e-2 (relative root-mean-square 1.0e-2),
+the same whole, in portions and decoding.
 """
 
 import numpy as np
