@@ -68,3 +68,27 @@ def test_warm_up_captures_graphs_and_gives_everything_back(tmp_path):
     runner.step([StepEntry(a, [1, 2, 3], [])])
     runner.step([StepEntry(a, [4], [0])])
     assert runner.graph_replays == before + 1          # the first decode step of a request replays a warmed graph
+
+
+def test_a_step_too_large_for_the_workspace_is_refused_and_holds_nothing(tmp_path):
+    """The step's arrays (here: block tables of many rows) do not fit the workspace: the step raises before
+    anything is launched, the pages it had reserved go back, and the runner carries on."""
+    from acorninfer_b200.engine.batch import BatchError, StepEntry
+    from acorninfer_b200.engine.runner import ModelRunner
+    d = make_model_dir(tmp_path / "m", TINY_B)
+    runner = ModelRunner.from_model_dir(d, dtype="float32", num_blocks=64, page_size=TINY_B["page_size"], max_requests=8,
+                                        workspace_ints=96)
+    V = TINY_B["cfg"].vocab_size
+    a = runner.open("a")
+    logits = runner.step([StepEntry(a, random_tokens(5, V, 1), [4])])        # small steps fit
+    assert logits.shape == (1, V)
+    free = runner.manager.free_pages()
+    others = [runner.open(i) for i in range(6)]
+    with pytest.raises(BatchError, match="workspace holds"):
+        runner.step([StepEntry(rc, random_tokens(9, V, 2), [8]) for rc in others])
+    assert runner.manager.free_pages() == free and all(rc.length == 0 and rc.tables == [[]] for rc in others)
+    again = runner.step([StepEntry(a, [7], [0])])
+    assert again.shape == (1, V)
+    for rc in [a] + others:
+        runner.close(rc)
+    runner.manager.assert_balanced()
