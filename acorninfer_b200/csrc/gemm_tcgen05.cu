@@ -104,9 +104,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     const int kb0 = (int)((int64_t)p.kblocks * split / splits), kb1 = (int)((int64_t)p.kblocks * (split + 1) / splits);
     const int nkb = kb1 - kb0;
 
-    // every CTA of the cluster says that it runs; the epilogue waits for all of them to have said
-    // so before it writes into their shared memory
-    if (splits > 1) cg::this_cluster().barrier_arrive();
+    // Where the receive buffer of the epilogue lies: beside the ring for tiles of up to 32 tokens, in
+    // the drained ring for larger ones (which buys them a deeper ring or a third CTA to the SM).
+    constexpr bool RECV_IN_RING = MB > 32;
+    // every CTA of the cluster says that it runs (or, with the buffer in the ring, that its ring is
+    // drained); the epilogue waits for all of them to have said so before it writes into their
+    // shared memory
+    if (splits > 1 && !RECV_IN_RING) cg::this_cluster().barrier_arrive();
     const int pre = nkb < STAGES ? nkb : STAGES;
     if (warp == 0) {
         // Barriers, then at once the weight tiles of the first stages: they do not depend on the
@@ -191,12 +195,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
     // memory straight into the receive buffers of their owners (remote shared-memory stores, which
     // do not wait), the cluster meets once, and each CTA adds up, in rank order, the partial rows
     // it received: recv[q][i][128] is row rank + i * csize as computed by rank q.  For tiles of up
-    // to 64 tokens the buffer lies outside the ring, because a peer may still be in its main loop
-    // when rows arrive; larger tiles are never split and use the drained ring.
+    // to 32 tokens the buffer lies outside the ring, because a peer may still be in its main loop
+    // when rows arrive; larger tiles use the ring, and a split one says when its ring is drained
+    // (its accumulator is complete: every stage has been read).
     constexpr int RED_FLOATS = TC_RED_FLOATS(MB);
     float* red = reinterpret_cast<float*>(bars + 2 * STAGES + 2);     // reduction scratch, then inv[MB]
     float* inv_s = red + RED_FLOATS;
-    float* recv = MB <= 64 ? inv_s + MB : reinterpret_cast<float*>(smem);
+    float* recv = RECV_IN_RING ? reinterpret_cast<float*>(smem) : inv_s + MB;
     int rank = 0, csize = 1;
     if (splits > 1) {
         cg::cluster_group cluster = cg::this_cluster();
@@ -204,7 +209,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tcgen05_kernel(const __grid_c
         csize = (int)cluster.num_blocks();
     }
     const int slots = (MB + csize - 1) / csize;
-    if (splits > 1) cg::this_cluster().barrier_wait();
+    if (splits > 1) {
+        if (RECV_IN_RING) cg::this_cluster().barrier_arrive();
+        cg::this_cluster().barrier_wait();
+    }
     {
         const uint32_t mine = tc_smem(recv) + (uint32_t)((rank * slots * TC_BM + warp * 32 + lane) * 4);
         int owner = 0, slot = 0;                                      // of row c + i
@@ -379,8 +387,8 @@ template <int MB, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t stream) {
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + MB * TC_BK * 2;
     const size_t ring = (size_t)STAGES * STAGE_BYTES;
-    const size_t part = (size_t)MB * TC_BM * sizeof(float);
-    const size_t recv = MB <= 64 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
+    const size_t part = (size_t)(MB + 8) * TC_BM * sizeof(float);       // the receive buffer, where it lies in the ring
+    const size_t recv = MB <= 32 ? (size_t)(MB + 8) * TC_BM * sizeof(float) : 0;      // see the kernel's epilogue
     const size_t smem = (ring > part ? ring : part) + (2 * STAGES + 2) * 8 +
                         (TC_RED_FLOATS(MB) + MB) * sizeof(float) + recv + 1024;
     static AcornPerDevice configured;
@@ -436,7 +444,7 @@ static int run_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, TcPara
     switch (mb) {
         case 16: return per_sm == 3 ? launch_tc<16, 3>(mw, mx, p, splits, stream) : launch_tc<16, 5>(mw, mx, p, splits, stream);
         case 32: return per_sm == 3 ? launch_tc<32, 2>(mw, mx, p, splits, stream) : launch_tc<32, 4>(mw, mx, p, splits, stream);
-        case 64: return launch_tc<64, 3>(mw, mx, p, splits, stream);
+        case 64: return per_sm == 3 ? launch_tc<64, 3>(mw, mx, p, splits, stream) : launch_tc<64, 4>(mw, mx, p, splits, stream);
         default: return launch_tc<128, 3>(mw, mx, p, splits, stream);
     }
 }

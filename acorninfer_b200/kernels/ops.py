@@ -599,7 +599,7 @@ def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148) -> tuple[int, int]:
     splits = 1
     while splits < 8 and tiles * splits * 2 <= 2 * num_sms and kblocks // (splits * 2) >= 4:
         splits *= 2
-    if rows <= 32 and splits == 1 and kblocks >= 8 and num_sms < tiles and tiles * 2 <= 3 * num_sms:
+    if rows <= 64 and splits == 1 and kblocks >= 8 and num_sms < tiles and tiles * 2 <= 3 * num_sms:
         return 2, 3                     # more tiles than SMs, fewer than 1.5 to an SM (measured: 36.0 -> 33.3 us)
     return splits, 2
 

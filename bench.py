@@ -423,6 +423,34 @@ def long_context(steps: int, warmup: int, pk: dict, torch) -> dict:
             "step_GB": round(step_bytes / 1e9, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 4)}
 
 
+def float32_path(pk: dict, torch) -> dict:
+    """The true 32-bit path at Qwen3-8B layer sizes with 4 of the 36 layers (float32 weights, cache
+    and products on the CUDA cores): a decode step at batch 8, context 4,096, and a 2,048-token
+    prefill, device-timed.  It is the correctness path; the figures say how long a check takes."""
+    from acorninfer_b200.config.model_config import Qwen3Config
+    from acorninfer_b200.engine.runner import ModelRunner
+
+    layers, B, steps, warmup = 4, 8, 8, 3
+    conf = dict(QWEN3_8B, num_hidden_layers=layers)
+    runner = ModelRunner.from_random(Qwen3Config(**conf), seed=0, sigma=0.02, dtype="float32",
+                                     num_blocks=B * CONTEXT // PAGE + 2 * (PROMPT // PAGE) + 64, page_size=PAGE,
+                                     max_requests=B + 2, max_step_tokens=4096)
+    for g in runner.manager.groups:
+        g.storage.normal_(0, 1)
+    nums = model_numbers(conf, layers)
+    res = time_decode(runner, None, B, steps, warmup, CONTEXT, torch)
+    step_bytes = 2 * (nums["weight_bytes"] + B * res["mean_context"] * nums["kv_bytes_per_token"])   # 4-byte elements
+    pre_ms = time_prefill(runner, PROMPT, 1, torch)
+    del runner
+    return {"model": "Qwen3-8B layer sizes, random weights, float32", "layers": layers,
+            "layers_of_config": QWEN3_8B["num_hidden_layers"], "batch": B, "context": CONTEXT,
+            "decode_ms_per_step": round(res["ms_per_step"], 3),
+            "decode_GBps": round(step_bytes / (res["ms_per_step"] / 1e3) / 1e9, 1),
+            "decode_frac_hbm": round(step_bytes / (res["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+            "prefill_tokens": PROMPT, "prefill_ms": round(pre_ms, 2),
+            "prefill_tflops": round(prefill_flops(nums, layers, PROMPT) / (pre_ms / 1e3) / 1e12, 2)}
+
+
 def reference_arm(args) -> int:
     """The unmodified reference (installed under baseline/_ref) through its own public API:
     ``from_pretrained`` + ``Engine.submit/step`` with its fastest documented settings (Triton paged
@@ -526,7 +554,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the batch of the headline value")
     ap.add_argument("--skip-extra", action="store_true",
-                    help="leave out the per-kernel table, the continuous-batching run and the long-context run")
+                    help="leave out the per-kernel table, the continuous-batching, long-context and float32 runs")
     args = ap.parse_args()
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
@@ -579,6 +607,9 @@ def main() -> int:
         gc.collect()
         torch.cuda.empty_cache()
         extra["long_context"] = long_context(min(args.steps, 32), 4, pk, torch)
+        gc.collect()
+        torch.cuda.empty_cache()
+        extra["float32_path"] = float32_path(pk, torch)
         points["cb_0.6b_128req_output_tok_s"] = extra["continuous_batching"]["output_tok_s"]
         points["decode_32b_b8_ctx16384"] = extra["long_context"]["tok_s"]
 

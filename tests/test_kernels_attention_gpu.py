@@ -88,12 +88,17 @@ def dense_attention(q, k, v, scale, window, q_start):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,d,P,window", [(4, 2, 16, 4, None), (10, 2, 48, 16, None), (8, 1, 128, 16, None),
-                                               (6, 3, 80, 8, 13), (5, 5, 32, 32, 40)])
+                                               (6, 3, 80, 8, 13), (5, 5, 32, 32, 40), (20, 2, 18, 16, None),
+                                               (3, 1, 200, 8, None), (24, 2, 36, 16, 700)])
 def test_attention_plain(dtype, nq, nkv, d, P, window):
-    before, qlens = [0, 300, 129, 16, 0], [150, 1, 2, 1, 1]
-    lay = rows_layout(before, qlens, P, 200, seed=2)
+    """Among the cases: more query heads to a kv head than one block takes (10, 12), head sizes whose rows
+    are not 16-byte aligned (18; 36 in bfloat16) or wider than the 128 lanes (200), a row of 1,100 keys
+    (three chunks of 512) and a window that starts inside the second chunk."""
+    before, qlens = [0, 300, 129, 16, 0, 1100], [150, 1, 2, 1, 1, 3]
+    num_pages = sum(-(-(b + n) // P) for b, n in zip(before, qlens)) + 7
+    lay = rows_layout(before, qlens, P, num_pages, seed=2)
     scale = d ** -0.5
-    k_pages = torch.zeros(200, nkv, P, d, device=DEV, dtype=dtype)
+    k_pages = torch.zeros(num_pages, nkv, P, d, device=DEV, dtype=dtype)
     v_pages = torch.zeros_like(k_pages)
     qs, wants = [], []
     for r, (b, n) in enumerate(zip(before, qlens)):

@@ -96,8 +96,11 @@ def test_swiglu_and_cast(dtype):
     assert torch.equal(ops().cast(x.to(torch.bfloat16), torch.float32), x.to(torch.bfloat16).float())
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (7, 331, 120), (130, 65, 33), (64, 64, 16), (3, 1000, 257)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (7, 331, 120), (130, 65, 33), (64, 64, 16), (3, 1000, 257),
+                                   (16, 100, 324), (17, 40, 1028), (65, 300, 200), (300, 130, 516)])
 def test_gemm_f32_is_true_float32(M, N, K):
+    """K a multiple of 4 takes the streaming kernel (up to 64 rows) or the 128 x 128 tile kernel, other K
+    the plain one; (17, 40, 1028) runs more k-steps than the streaming kernel's ring has stages."""
     a = torch.randn(M, K, device=DEV)
     w = torch.randn(N, K, device=DEV)
     out = ops().gemm_f32(a, w)
@@ -105,6 +108,25 @@ def test_gemm_f32_is_true_float32(M, N, K):
     assert torch.allclose(out.double(), want, atol=1e-5 * math.sqrt(K), rtol=1e-5)
     # a row's result does not depend on the other rows
     assert torch.equal(ops().gemm_f32(a[:1].contiguous(), w)[0], out[0])
+
+
+def test_gemm_f32_gives_the_same_bits_from_each_of_its_kernels():
+    """A row's result is one chain of fused multiply-adds in the order of K in every kernel: the
+    streaming kernel (8 rows), the tile kernel (200 rows) and the plain kernel (operands whose rows
+    are not 16-byte aligned) agree bit for bit, also where tiles end inside the matrix."""
+    M, N, K = 200, 333, 712
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    tile = ops().gemm_f32(a, w)
+    rows = ops().gemm_f32(a[:8].contiguous(), w)
+    assert torch.equal(rows, tile[:8])
+    mid = ops().gemm_f32(a[100:140].contiguous(), w)            # 40 rows: three row blocks of the streaming kernel
+    assert torch.equal(mid, tile[100:140])
+    a_odd = torch.zeros(M, K + 1, device=DEV)[:, :K]            # row stride K + 1: the plain kernel
+    a_odd.copy_(a)
+    assert a_odd.stride(0) % 4 != 0
+    assert torch.equal(ops().gemm_f32(a_odd, w), tile)
+    assert torch.allclose(tile.double(), a.double() @ w.double().T, atol=1e-5 * math.sqrt(K), rtol=1e-5)
 
 
 def test_gemm_f32_shows_what_a_reduced_precision_mode_would_hide():
