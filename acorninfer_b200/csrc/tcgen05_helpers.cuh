@@ -15,6 +15,7 @@
 #define ACORN_KERNEL_GEMM_TC 1
 #define ACORN_KERNEL_ATTN_PREFILL_TC 2
 #define ACORN_KERNEL_ATTN_DECODE_TMA 3
+#define ACORN_KERNEL_GEMM_PAIR 4
 #define ACORN_KERNEL_SELFTEST 9
 
 static __device__ int* g_error_word = nullptr;

@@ -51,7 +51,7 @@ def _load():
 
 
 _error_word: ctypes.c_int | None = None       # pinned host memory that kernels write when a bounded wait gives up
-_KERNEL_NAMES = {1: "gemm_tcgen05", 2: "attention_prefill_tc", 3: "attention_decode_tma", 9: "error-word self-test"}
+_KERNEL_NAMES = {1: "gemm_tcgen05", 2: "attention_prefill_tc", 3: "attention_decode_tma", 4: "gemm_tcgen05_pair", 9: "error-word self-test"}
 
 
 def _init_error_word(library) -> None:
@@ -61,7 +61,8 @@ def _init_error_word(library) -> None:
     if code != 0 or not host.value:
         raise KernelError(f"could not allocate the kernels' error word: CUDA error {code}")
     for setter in ("acorn_gemm_tc_set_error_word", "acorn_attention_tc_set_error_word",
-                   "acorn_attention_decode_tma_set_error_word", "acorn_selftest_set_error_word"):
+                   "acorn_attention_decode_tma_set_error_word", "acorn_selftest_set_error_word",
+                   "acorn_gemm_tc_pair_set_error_word"):
         code = getattr(library, setter)(dev)
         if code != 0:
             raise KernelError(f"{setter}: CUDA error {code}")
@@ -75,7 +76,7 @@ def raise_on_kernel_error() -> None:
         return
     word = _error_word.value
     _error_word.value = 0
-    for getter in (gemm_tc_error, attention_tc_error, attention_decode_tma_error):      # clear the kernels' own flags
+    for getter in (gemm_tc_error, attention_tc_error, attention_decode_tma_error, gemm_tc_pair_error):   # clear the kernels' own flags
         getter()
     raise KernelError(f"kernel {_KERNEL_NAMES.get(word // 100, word // 100)} gave up a bounded wait at point "
                       f"{word % 100}: the results of the step are not valid")
@@ -126,6 +127,8 @@ class _Sigs:
                               c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
+    acorn_gemm_tc_pair = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_gemm_tc_pair_error = []
     acorn_gemm_tc_error = []
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
     acorn_sample = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -138,6 +141,7 @@ class _Sigs:
     acorn_attention_tc_set_error_word = [c_void_p]
     acorn_attention_decode_tma_set_error_word = [c_void_p]
     acorn_selftest_set_error_word = [c_void_p]
+    acorn_gemm_tc_pair_set_error_word = [c_void_p]
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -751,6 +755,29 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
     if epilogue is not None:
         return NormedRows(out, ss_out, epilogue.eps, N)
     return out
+
+
+def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, pairs: int | None = None) -> torch.Tensor:
+    """x [M, K] @ w [N, K]^T in bfloat16 on pairs of CTAs (tcgen05 ``cta_group::2``), for many rows:
+    tiles of 256 rows of ``w`` by 256 rows of ``x``, one pair of SMs to a tile at a time."""
+    if not gemm_tc_supported(x, w):
+        raise KernelError(f"gemm_tc_pair does not take x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
+                          f"w {tuple(w.shape)} {w.dtype}: bf16, K contiguous, K and strides multiples of 8")
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _check(out, "out", torch.bfloat16, 2)
+    if pairs is None:
+        pairs = device_sms(x.device) // 2
+    _ok(lib().acorn_gemm_tc_pair(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+                                 M, N, K, int(pairs), _stream()), "gemm_tc_pair", f"{M}x{N}x{K}")
+    return out
+
+
+def gemm_tc_pair_error() -> int:
+    """0, or where a bounded wait inside the paired tcgen05 GEMM gave up since the last call (clears it)."""
+    return int(lib().acorn_gemm_tc_pair_error())
 
 
 def gemm_tc_error() -> int:
