@@ -216,3 +216,26 @@ extern "C" int acorn_qk_rope_kv(void* qkv, const float* q_w, const float* k_w, c
         pairing, P, eps, write_kv));
     return ACORN_ERR_UNSUPPORTED;
 }
+
+// cos and sin of position * inv_freq[j] for every token of a step: out[t][j] = cos, out[t][half + j] = sin
+// (float32, the accurate sincosf).  One table serves every layer of the step.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ out, int tokens, int half) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)tokens * half) return;
+    const int t = (int)(i / half), j = (int)(i - (int64_t)t * half);
+    float s, c;
+    sincosf((float)positions[t] * inv_freq[j], &s, &c);
+    out[(int64_t)t * 2 * half + j] = c;
+    out[(int64_t)t * 2 * half + half + j] = s;
+}
+
+extern "C" int acorn_rope_table(const int* positions, const float* inv_freq, float* out, int tokens, int half,
+                                cudaStream_t stream) {
+    if (tokens <= 0 || half <= 0) return 0;
+    const int64_t n = (int64_t)tokens * half;
+    return acorn_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, positions, inv_freq,
+                        out, tokens, half);
+}

@@ -127,7 +127,13 @@ class _Sigs:
                               c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     acorn_gemm_tc_supported = [c_int64, c_int64, c_int64, c_int64, c_int64]
-    acorn_gemm_tc_pair = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]
+    acorn_gemm_tc_pair = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
+    acorn_gemm_tc_pair_qkv_rope = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
+                                   c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                   c_void_p]
+    acorn_rope_table = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     acorn_gemm_tc_pair_error = []
     acorn_gemm_tc_error = []
     acorn_gemm_f32 = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
@@ -615,6 +621,9 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
 # At or below this many rows the tcgen05 kernel (weights on the 128-row side of the MMA) streams the
 # weight matrix at least as fast as the library product; above it the library's larger tiles win.
 GEMM_TC_MAX_ROWS = 32
+# From this many rows on, the paired kernel (256 x 256 tiles over two SMs, fused epilogues) is used.
+import os as _os
+GEMM_PAIR_MIN_ROWS = int(_os.environ.get("ACORN_PAIR_ROWS", "65"))
 
 
 @dataclass
@@ -659,6 +668,17 @@ class RopeKvEpilogue:
     num_heads: int
     num_kv_heads: int
     eps: float
+    cos_sin: torch.Tensor | None = None      # [M, 128] float32 from ``rope_table``: spares the epilogue its sincosf
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[tokens, 2 * len(inv_freq)] float32: cos, then sin, of position * inv_freq for every token."""
+    _check(positions, "positions", torch.int32, 1)
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    T, half = positions.numel(), inv_freq.numel()
+    out = torch.empty((T, 2 * half), dtype=torch.float32, device=positions.device)
+    _ok(lib().acorn_rope_table(positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), T, half, _stream()), "rope_table")
+    return out
 
 
 def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -669,9 +689,9 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
     nq, nkv = ep.num_heads, ep.num_kv_heads
     M, K = xt.shape
     N = (nq + 2 * nkv) * 128
-    if not gemm_tc_supported(xt, w) or w.shape[0] != N or M > GEMM_TC_MAX_ROWS:
+    if not gemm_tc_supported(xt, w) or w.shape[0] != N or not fused_rows_ok(M, xt.dtype):
         raise KernelError(f"gemm_tc_qkv_rope does not take x {tuple(xt.shape)} {xt.dtype}, w {tuple(w.shape)} {w.dtype} "
-                          f"for {nq}/{nkv} heads of 128 (at most {GEMM_TC_MAX_ROWS} rows)")
+                          f"for {nq}/{nkv} heads of 128 (at most {GEMM_TC_MAX_ROWS} or at least {GEMM_PAIR_MIN_ROWS} rows)")
     _check(ep.positions, "positions", torch.int32, 1)
     _check(ep.inv_freq, "inv_freq", torch.float32, 1)
     if ep.inv_freq.numel() != 64 or ep.positions.numel() < M:
@@ -690,6 +710,21 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=xt.device)
     _check(out, "out", torch.bfloat16, 2)
+    if M > GEMM_TC_MAX_ROWS:
+        if ep.cos_sin is not None:
+            _check(ep.cos_sin, "cos_sin", torch.float32, 2)
+            if tuple(ep.cos_sin.shape) != (M, 128) or not ep.cos_sin.is_contiguous():
+                raise KernelError("gemm_tc_qkv_rope: cos_sin must be contiguous [rows, 128]")
+        _ok(lib().acorn_gemm_tc_pair_qkv_rope(
+            xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, K,
+            device_sms(xt.device) // 2,
+            rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
+            rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
+            ep.positions.data_ptr(), _ptr(ep.token_row), _ptr(ep.block_table), _ptr(ep.page_base),
+            ep.block_table.stride(0) if ep.block_table is not None else 0, _ptr(ep.k_pages), _ptr(ep.v_pages),
+            _ptr(ep.q_weight32), _ptr(ep.k_weight32), ep.inv_freq.data_ptr(), _ptr(ep.cos_sin), nq, nkv, P, float(ep.eps),
+            _stream()), "gemm_tc_pair_qkv_rope", f"{M}x{N}x{K}")
+        return out
     splits, per_sm = gemm_tc_plan(M, N, K, device_sms(xt.device))
     _ok(lib().acorn_gemm_tc_qkv_rope(
         xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, K, splits, per_sm,
@@ -757,21 +792,48 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits:
     return out
 
 
-def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, pairs: int | None = None) -> torch.Tensor:
+def gemm_tc_pair(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: torch.Tensor | None = None,
+                 epilogue: AddNormEpilogue | None = None, swiglu: bool = False, pairs: int | None = None):
     """x [M, K] @ w [N, K]^T in bfloat16 on pairs of CTAs (tcgen05 ``cta_group::2``), for many rows:
-    tiles of 256 rows of ``w`` by 256 rows of ``x``, one pair of SMs to a tile at a time."""
-    if not gemm_tc_supported(x, w):
-        raise KernelError(f"gemm_tc_pair does not take x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
+    tiles of 256 rows of ``x`` by 256 rows of ``w``, one pair of SMs to a tile at a time.  ``x`` as
+    ``NormedRows``, ``epilogue`` and ``swiglu`` as in ``gemm_tc``."""
+    rows = x if isinstance(x, NormedRows) else None
+    xt = rows.x if rows is not None else x
+    if not gemm_tc_supported(xt, w):
+        raise KernelError(f"gemm_tc_pair does not take x {tuple(xt.shape)} {xt.dtype} stride {xt.stride()}, "
                           f"w {tuple(w.shape)} {w.dtype}: bf16, K contiguous, K and strides multiples of 8")
-    M, K = x.shape
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tc_pair writes bfloat16 or float32")
+    M, K = xt.shape
     N = w.shape[0]
+    mode, resid, ldr, norm_w, ss_out = 0, None, 0, None, None
+    out_cols = N
+    if epilogue is not None:
+        if swiglu or out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc_pair: the add-norm epilogue writes bfloat16 and excludes SwiGLU")
+        _check(epilogue.resid32, "resid32", torch.float32, 2)
+        _check(epilogue.weight32, "norm weight", torch.float32, 1)
+        if epilogue.resid32.shape != (M, N) or epilogue.weight32.numel() != N:
+            raise KernelError("gemm_tc_pair: residual / norm weight do not match the product's shape")
+        mode, resid, ldr, norm_w = 1, epilogue.resid32, epilogue.resid32.stride(0), epilogue.weight32
+        ss_out = torch.empty((2 * -(-N // 256), M), dtype=torch.float32, device=xt.device)
+    elif swiglu:
+        if N % 128 or out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc_pair: SwiGLU epilogue needs N a multiple of 128 and bfloat16 output")
+        mode, out_cols = 2, N // 2
     if out is None:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    _check(out, "out", torch.bfloat16, 2)
+        out = torch.empty((M, out_cols), dtype=out_dtype, device=xt.device)
+    _check(out, "out", out_dtype, 2)
     if pairs is None:
-        pairs = device_sms(x.device) // 2
-    _ok(lib().acorn_gemm_tc_pair(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-                                 M, N, K, int(pairs), _stream()), "gemm_tc_pair", f"{M}x{N}x{K}")
+        pairs = device_sms(xt.device) // 2
+    _ok(lib().acorn_gemm_tc_pair(
+        xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+        1 if out_dtype == torch.float32 else 0, int(pairs), mode,
+        rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
+        rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
+        _ptr(resid), ldr, _ptr(norm_w), _ptr(ss_out), _stream()), "gemm_tc_pair", f"{M}x{N}x{K}")
+    if epilogue is not None:
+        return NormedRows(out, ss_out, epilogue.eps, N)
     return out
 
 
@@ -786,8 +848,9 @@ def gemm_tc_error() -> int:
 
 
 def fused_rows_ok(num_rows: int, dtype: torch.dtype) -> bool:
-    """Whether products of this many rows run on the tcgen05 kernel with fused norm epilogues."""
-    return dtype == torch.bfloat16 and 0 < num_rows <= GEMM_TC_MAX_ROWS
+    """Whether products of this many rows run on a tcgen05 kernel of this library with fused epilogues:
+    the one-CTA kernel up to ``GEMM_TC_MAX_ROWS`` rows, the paired kernel from ``GEMM_PAIR_MIN_ROWS`` on."""
+    return dtype == torch.bfloat16 and (0 < num_rows <= GEMM_TC_MAX_ROWS or num_rows >= GEMM_PAIR_MIN_ROWS)
 
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: AddNormEpilogue | None = None,
@@ -810,8 +873,11 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
     out_dtype = out_dtype or xt.dtype
     if fused:
         if not (fused_rows_ok(xt.shape[0], xt.dtype) and gemm_tc_supported(xt, w)):
-            raise KernelError(f"linear: fused epilogues need the tcgen05 path (bf16, <= {GEMM_TC_MAX_ROWS} rows, "
-                              f"K a multiple of 8); got {tuple(xt.shape)} {xt.dtype} x {tuple(w.shape)} {w.dtype}")
+            raise KernelError(f"linear: fused epilogues need a tcgen05 path (bf16, <= {GEMM_TC_MAX_ROWS} or >= "
+                              f"{GEMM_PAIR_MIN_ROWS} rows, K a multiple of 8); got {tuple(xt.shape)} {xt.dtype} x "
+                              f"{tuple(w.shape)} {w.dtype}")
+        if xt.shape[0] > GEMM_TC_MAX_ROWS:
+            return gemm_tc_pair(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
         return gemm_tc(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
     if w.dtype == torch.float32:
         y = gemm_f32(cast(x, torch.float32) if x.dtype != torch.float32 else x, w)
@@ -820,6 +886,8 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
         raise KernelError(f"linear: unsupported dtypes x={x.dtype}, w={w.dtype}")
     if x.shape[0] <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w):
         return gemm_tc(x, w, out_dtype)
+    if x.shape[0] >= GEMM_PAIR_MIN_ROWS and gemm_tc_supported(x, w):
+        return gemm_tc_pair(x, w, out_dtype)
     if _TIMER is not None:
         _TIMER.begin()
     try:

@@ -89,7 +89,8 @@ class Attention(Mixer):
                 inputs.positions, inputs.token_row, g.block_table, g.page_base,
                 cache.k_pages if cache.write else None, cache.v_pages if cache.write else None,
                 self.q_norm32, self.k_norm32, pos.inv_freq, self.nq, self.nkv,
-                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0))
+                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
+                cos_sin=pos.table(inputs) if rows > ops.GEMM_TC_MAX_ROWS and hasattr(pos, "table") else None))
         else:
             qkv = ops.linear(x, self.w_qkv, out_dtype=self.ctx.dtype)
             ops.qk_rope_kv(qkv, self.q_norm32, self.k_norm32,

@@ -37,6 +37,15 @@ class Rope(PositionEncoding):
             self._inv_freq_dev = self._inv_freq_cpu.to(self.ctx.device).contiguous()
         return self._inv_freq_dev
 
+    def table(self, inputs) -> torch.Tensor:
+        """cos and sin of every token's angles, [tokens, rotary_dim] float32 (cos, then sin): computed by
+        the first layer of a step that asks and kept with the step's inputs for the others."""
+        from ..kernels import ops
+        key = ("rope.table", self.theta, self.rotary_dim)
+        if key not in inputs.extra:
+            inputs.extra[key] = ops.rope_table(inputs.positions, self.inv_freq)
+        return inputs.extra[key]
+
 
 @POSITION_ENCODINGS.register("none")
 class NoPosition(PositionEncoding):
