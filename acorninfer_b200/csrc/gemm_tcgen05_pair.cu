@@ -23,8 +23,12 @@
 // 64 contiguous bytes at a time.
 //
 // Tiles are taken round robin (pair p: tiles p, p + pairs, ...), the token tiles of one W tile next
-// to one another, so that a W tile comes from DRAM once.  Every wait is bounded and reports through
-// the error word; the two CTAs meet at a cluster barrier before either frees its tensor memory.
+// to one another, so that a W tile comes from DRAM once and the pairs that share it read it together.
+// (Sharing the work out by k-steps instead, with partial tiles handed over through global memory, was
+// built and measured: pairs that run out of step with one another lose the shared reads, and handing
+// partial tiles over at the end of a product cost more than the idle SMs of a last, partly filled round.)
+// Every wait is bounded and reports through the error word; the two CTAs meet at a cluster barrier
+// before either frees its tensor memory.
 #include "tcgen05_helpers.cuh"
 
 #define G2_BT 128            // tokens a CTA (lanes of its tensor memory)
@@ -277,12 +281,14 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(free_bar0 + 8 * as);
             };
+            // 32 columns of this thread's token
+            auto load_cols = [&](int c, float (&v)[32]) { tmem_ld32(taddr + c, v); };
 
             if (p.mode == G2_MODE_PLAIN) {
 #pragma unroll 1
                 for (int c = half * 128; c < half * 128 + 128; c += 32) {
                     float v[32];
-                    tmem_ld32(taddr + c, v);
+                    load_cols(c, v);
                     if (c + 32 == half * 128 + 128) release();
                     const int nv = p.N - (n0 + c);
                     if (m_ok && nv > 0) {
@@ -299,8 +305,8 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
 #pragma unroll 1
                     for (int c = 0; c < 64; c += 32) {
                         float gt[32], up[32];
-                        tmem_ld32(taddr + b * 128 + c, gt);
-                        tmem_ld32(taddr + b * 128 + 64 + c, up);
+                        load_cols(b * 128 + c, gt);
+                        load_cols(b * 128 + 64 + c, up);
                         if (c == 32) release();
                         const int oc = tn * 128 + b * 64 + c;
                         const int nv = p.N / 2 - oc;
@@ -319,7 +325,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
 #pragma unroll 1
                 for (int c = half * 128; c < half * 128 + 128; c += 32) {
                     float v[32];
-                    tmem_ld32(taddr + c, v);
+                    load_cols(c, v);
                     if (c + 32 == half * 128 + 128) release();
                     const int nv = p.N - (n0 + c);
                     if (m_ok && nv > 0) {
@@ -380,7 +386,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
                             dst = (is_k ? p.k_pages : p.v_pages) +
                                   ((((int64_t)page * p.nkv + kvh) << p.logP) + (pos & ((1 << p.logP) - 1))) * 128;
                     }
-                    const uint32_t th = taddr + hh * 128;
+                    const int th = hh * 128;
                     if (is_q || is_k) {
                         float rinv = 1.f;
                         if (hw != nullptr) {
@@ -388,7 +394,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
 #pragma unroll 1
                             for (int c = 0; c < 128; c += 32) {
                                 float v[32];
-                                tmem_ld32(th + c, v);
+                                load_cols(th + c, v);
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) ss += (v[j] * inv) * (v[j] * inv);
                             }
@@ -397,8 +403,8 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
 #pragma unroll 1
                         for (int c = 0; c < 64; c += 32) {
                             float lo[32], hi[32];
-                            tmem_ld32(th + c, lo);
-                            tmem_ld32(th + 64 + c, hi);
+                            load_cols(th + c, lo);
+                            load_cols(th + 64 + c, hi);
                             if (dst != nullptr) {
                                 const float4* cs4 = p.cos_sin != nullptr
                                     ? reinterpret_cast<const float4*>(p.cos_sin + (int64_t)m * 128 + c) : nullptr;
@@ -430,7 +436,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
 #pragma unroll 1
                         for (int c = 0; c < 128; c += 32) {
                             float v[32];
-                            tmem_ld32(th + c, v);
+                            load_cols(th + c, v);
                             if (dst != nullptr) {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) v[j] *= inv;

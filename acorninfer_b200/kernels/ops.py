@@ -621,9 +621,22 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
 # At or below this many rows the tcgen05 kernel (weights on the 128-row side of the MMA) streams the
 # weight matrix at least as fast as the library product; above it the library's larger tiles win.
 GEMM_TC_MAX_ROWS = 32
-# From this many rows on, the paired kernel (256 x 256 tiles over two SMs, fused epilogues) is used.
-import os as _os
-GEMM_PAIR_MIN_ROWS = int(_os.environ.get("ACORN_PAIR_ROWS", "65"))
+# The paired kernel (256 x 256 tiles, a pair of SMs to a tile at a time, fused epilogues) is used from
+# this many rows on, where its tiles fill the device: see ``pair_rows_ok``.
+GEMM_PAIR_MIN_ROWS = 256
+GEMM_PAIR_MIN_FILL = 0.8
+
+
+def pair_rows_ok(num_rows: int, width: int, num_sms: int = 148) -> bool:
+    """Whether a product of ``num_rows`` rows and ``width`` output columns suits the paired kernel: its
+    tiles of 256 x 256 are taken in rounds of one tile to a pair of SMs, and the rounds must be filled to
+    ``GEMM_PAIR_MIN_FILL`` on average (128 tiles on 74 pairs: two rounds, 0.86; 96 tiles: two rounds,
+    0.65, where the library's choice of tile shapes is faster)."""
+    if num_rows < GEMM_PAIR_MIN_ROWS:
+        return False
+    pairs = max(num_sms // 2, 1)
+    tiles = -(-num_rows // 256) * -(-width // 256)
+    return tiles / (-(-tiles // pairs) * pairs) >= GEMM_PAIR_MIN_FILL
 
 
 @dataclass
@@ -689,9 +702,9 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
     nq, nkv = ep.num_heads, ep.num_kv_heads
     M, K = xt.shape
     N = (nq + 2 * nkv) * 128
-    if not gemm_tc_supported(xt, w) or w.shape[0] != N or not fused_rows_ok(M, xt.dtype):
+    if not gemm_tc_supported(xt, w) or w.shape[0] != N:
         raise KernelError(f"gemm_tc_qkv_rope does not take x {tuple(xt.shape)} {xt.dtype}, w {tuple(w.shape)} {w.dtype} "
-                          f"for {nq}/{nkv} heads of 128 (at most {GEMM_TC_MAX_ROWS} or at least {GEMM_PAIR_MIN_ROWS} rows)")
+                          f"for {nq}/{nkv} heads of 128")
     _check(ep.positions, "positions", torch.int32, 1)
     _check(ep.inv_freq, "inv_freq", torch.float32, 1)
     if ep.inv_freq.numel() != 64 or ep.positions.numel() < M:
@@ -715,9 +728,9 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
             _check(ep.cos_sin, "cos_sin", torch.float32, 2)
             if tuple(ep.cos_sin.shape) != (M, 128) or not ep.cos_sin.is_contiguous():
                 raise KernelError("gemm_tc_qkv_rope: cos_sin must be contiguous [rows, 128]")
+        pairs = device_sms(xt.device) // 2
         _ok(lib().acorn_gemm_tc_pair_qkv_rope(
-            xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, K,
-            device_sms(xt.device) // 2,
+            xt.data_ptr(), xt.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, K, pairs,
             rows.ss.data_ptr() if rows is not None else None, rows.ss.shape[0] if rows is not None else 0,
             rows.width if rows is not None else 0, float(rows.eps) if rows is not None else 0.0,
             ep.positions.data_ptr(), _ptr(ep.token_row), _ptr(ep.block_table), _ptr(ep.page_base),
@@ -738,8 +751,9 @@ def gemm_tc_qkv_rope(x, w: torch.Tensor, ep: RopeKvEpilogue, out: torch.Tensor |
 
 
 def rope_kv_fusable(num_rows: int, dtype: torch.dtype, head_dim: int, rotary_dim: int, interleaved: bool) -> bool:
-    """Whether the q/k/v product of such a layer can take ``RopeKvEpilogue`` for this many rows."""
-    return fused_rows_ok(num_rows, dtype) and head_dim == 128 and rotary_dim == 128 and not interleaved
+    """Whether the q/k/v product of such a layer can take ``RopeKvEpilogue`` (the row count is the
+    caller's to check with ``fused_rows_ok``)."""
+    return dtype == torch.bfloat16 and num_rows > 0 and head_dim == 128 and rotary_dim == 128 and not interleaved
 
 
 def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, splits: int | None = None,
@@ -847,10 +861,19 @@ def gemm_tc_error() -> int:
     return int(lib().acorn_gemm_tc_error())
 
 
-def fused_rows_ok(num_rows: int, dtype: torch.dtype) -> bool:
+def fused_rows_ok(num_rows: int, dtype: torch.dtype, widths=None, num_sms: int = 148) -> bool:
     """Whether products of this many rows run on a tcgen05 kernel of this library with fused epilogues:
-    the one-CTA kernel up to ``GEMM_TC_MAX_ROWS`` rows, the paired kernel from ``GEMM_PAIR_MIN_ROWS`` on."""
-    return dtype == torch.bfloat16 and (0 < num_rows <= GEMM_TC_MAX_ROWS or num_rows >= GEMM_PAIR_MIN_ROWS)
+    the one-CTA kernel up to ``GEMM_TC_MAX_ROWS`` rows; for more rows the paired kernel, where every
+    product of the part (``widths``: their output columns, one number or several) fills the device
+    (``pair_rows_ok``)."""
+    if dtype != torch.bfloat16 or num_rows <= 0:
+        return False
+    if num_rows <= GEMM_TC_MAX_ROWS:
+        return True
+    if widths is None:
+        return False
+    widths = (widths,) if isinstance(widths, int) else tuple(widths)
+    return all(pair_rows_ok(num_rows, w, num_sms) for w in widths)
 
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: AddNormEpilogue | None = None,
@@ -858,12 +881,13 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
     """x [T, K] times w [N, K] transposed.
 
     float32 operands: the CUDA-core kernel (no reduced-precision matrix mode).
-    bfloat16 operands: up to GEMM_TC_MAX_ROWS rows the tcgen05/TMA kernel of this library, above
-    that the library matrix product (cuBLAS); float32 accumulation either way, and
+    bfloat16 operands: up to GEMM_TC_MAX_ROWS rows the one-CTA tcgen05/TMA kernel of this library,
+    above that the library matrix product (cuBLAS); float32 accumulation either way, and
     ``out_dtype=float32`` keeps the accumulator's precision (used for logits).
     A weight stored in float32 under a bfloat16 engine is multiplied in float32.
-    ``x`` as ``NormedRows``, ``epilogue`` and ``swiglu`` exist on the tcgen05 path only
-    (``fused_rows_ok``); asking for them elsewhere is an error, not a silent detour.
+    ``x`` as ``NormedRows``, ``epilogue`` and ``swiglu`` exist on the tcgen05 kernels only: the one-CTA
+    kernel up to GEMM_TC_MAX_ROWS rows, the paired kernel above (callers ask ``fused_rows_ok`` whether
+    that pays for their sizes); asking for them with other operands is an error, not a silent detour.
     ``residual32`` ([T, N] float32) is an offer: where the product goes to the library it is
     added to ``residual32`` in place, in float32 (the library's C operand: the product is not
     rounded first), and None is returned; elsewhere the offer is ignored and the product returned.
@@ -872,10 +896,9 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
     xt = x.x if isinstance(x, NormedRows) else x
     out_dtype = out_dtype or xt.dtype
     if fused:
-        if not (fused_rows_ok(xt.shape[0], xt.dtype) and gemm_tc_supported(xt, w)):
-            raise KernelError(f"linear: fused epilogues need a tcgen05 path (bf16, <= {GEMM_TC_MAX_ROWS} or >= "
-                              f"{GEMM_PAIR_MIN_ROWS} rows, K a multiple of 8); got {tuple(xt.shape)} {xt.dtype} x "
-                              f"{tuple(w.shape)} {w.dtype}")
+        if not (xt.dtype == torch.bfloat16 and gemm_tc_supported(xt, w)):
+            raise KernelError(f"linear: fused epilogues need a tcgen05 path (bf16, K a multiple of 8); got "
+                              f"{tuple(xt.shape)} {xt.dtype} x {tuple(w.shape)} {w.dtype}")
         if xt.shape[0] > GEMM_TC_MAX_ROWS:
             return gemm_tc_pair(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
         return gemm_tc(x, w, out_dtype, epilogue=epilogue, swiglu=swiglu)
@@ -886,8 +909,6 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, epilogue: A
         raise KernelError(f"linear: unsupported dtypes x={x.dtype}, w={w.dtype}")
     if x.shape[0] <= GEMM_TC_MAX_ROWS and gemm_tc_supported(x, w):
         return gemm_tc(x, w, out_dtype)
-    if x.shape[0] >= GEMM_PAIR_MIN_ROWS and gemm_tc_supported(x, w):
-        return gemm_tc_pair(x, w, out_dtype)
     if _TIMER is not None:
         _TIMER.begin()
     try:

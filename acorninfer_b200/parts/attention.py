@@ -74,8 +74,12 @@ class Attention(Mixer):
         return attn_kernels.STEP_ARRAYS
 
     def fusable(self, num_rows):
-        return (ops.fused_rows_ok(num_rows, self.ctx.dtype) and self.w_qkv.dtype == torch.bfloat16
+        return (self._rows_fuse(num_rows) and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and (self.nq * self.d) % 8 == 0)
+
+    def _rows_fuse(self, num_rows):
+        widths = ((self.nq + 2 * self.nkv) * self.d, self.hidden_size)         # of the q/k/v product and of the o product
+        return ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
 
     def forward(self, x, inputs, cache, epilogue=None, residual32=None):
         g = inputs.groups[cache.group]
@@ -83,8 +87,9 @@ class Attention(Mixer):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
         if (pos is not None and self.w_qkv.dtype == torch.bfloat16 and ops.gemm_tc_supported(
                 x.x if isinstance(x, ops.NormedRows) else x, self.w_qkv)
+                and self._rows_fuse(rows)
                 and ops.rope_kv_fusable(rows, self.ctx.dtype, self.d, pos.rotary_dim, pos.interleaved)):
-            # few rows, head size 128: norm, rotation and the cache write are the epilogue of the product
+            # few rows or very many, head size 128: norm, rotation and the cache write are the epilogue of the product
             qkv = ops.gemm_tc_qkv_rope(x, self.w_qkv, ops.RopeKvEpilogue(
                 inputs.positions, inputs.token_row, g.block_table, g.page_base,
                 cache.k_pages if cache.write else None, cache.v_pages if cache.write else None,

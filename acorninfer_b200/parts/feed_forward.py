@@ -43,7 +43,9 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def fusable(self, num_rows):
-        return (ops.fused_rows_ok(num_rows, self.ctx.dtype) and self.w_gate_up.dtype == torch.bfloat16
+        widths = (2 * self.intermediate_size, self.hidden_size)                 # of the gate/up product and of the down product
+        return (ops.fused_rows_ok(num_rows, self.ctx.dtype, widths, ops.device_sms(self.ctx.device))
+                and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0)
 

@@ -149,3 +149,102 @@ def test_gemm_tc_qkv_rope_epilogue(nq, nkv, K, qlens, norm, write):
     a, b = q[..., :64], q[..., 64:]
     want = torch.cat([a * c - b * s_, b * c + a * s_], dim=-1).reshape(T, nq * d)
     assert torch.allclose(out[:, :nq * d].double().cpu(), want, atol=3e-2, rtol=2e-2)
+
+
+# ---------------------------------------------------------------------------- the paired kernel
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 8), (256, 256, 64), (300, 504, 200), (513, 1000, 4160), (40, 6144, 512),
+                                   (700, 264, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tc_pair_matches_float64(M, N, K, out_dtype):
+    """The pair-of-CTAs kernel alone: tiles that end inside the matrix in both directions, a K that is no
+    multiple of the stage, more tiles than pairs of SMs (700 x 264 with two pairs), one row."""
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    for pairs in (None, 2):
+        out = ops().gemm_tc_pair(x, w, out_dtype, pairs=pairs)
+        assert ops().gemm_tc_pair_error() == 0
+        tol = dict(atol=2e-2, rtol=2e-2) if out_dtype == torch.bfloat16 else dict(atol=1e-4, rtol=1e-4)
+        assert torch.allclose(out.double(), want, **tol)
+    assert torch.equal(ops().gemm_tc_pair(x, w, out_dtype), out)             # the same sums whatever the number of pairs
+
+
+@pytest.mark.parametrize("M,H,I", [(64, 256, 192), (300, 1024, 1536), (700, 200, 320)])
+def test_gemm_tc_pair_epilogues(M, H, I):
+    """SwiGLU and add + norm sums with rows that arrive un-normalised, against float64; widths that are
+    no multiple of the 256-column tile (200: the second half of the only tile is empty)."""
+    from acorninfer_b200.kernels.ops import AddNormEpilogue, NormedRows
+    torch.manual_seed(M)
+    x = (torch.randn(M, H, device=DEV) * 0.5).to(torch.bfloat16)
+    wgu = (torch.randn(2 * I, H, device=DEV) / H ** 0.5).to(torch.bfloat16)
+    ss = (torch.rand(5, M, device=DEV) + 0.5) * H
+    inv = torch.rsqrt(ss.double().sum(0) / H + 1e-6)
+    got = ops().gemm_tc_pair(NormedRows(x, ss, 1e-6, H), wgu, swiglu=True)
+    gu = ((x.double() @ wgu.double().T) * inv[:, None]).view(M, I // 64, 2, 64)
+    g, u = gu[:, :, 0].reshape(M, I), gu[:, :, 1].reshape(M, I)
+    assert got.shape == (M, I)
+    assert torch.allclose(got.double(), g * torch.sigmoid(g) * u, atol=2e-2, rtol=2e-2)
+    h = (torch.randn(M, I, device=DEV) * 0.5).to(torch.bfloat16)
+    wd = (torch.randn(H, I, device=DEV) / I ** 0.5).to(torch.bfloat16)
+    resid = torch.randn(M, H, device=DEV)
+    nw = torch.rand(H, device=DEV) + 0.5
+    r = resid.clone()
+    rows = ops().gemm_tc_pair(h, wd, epilogue=AddNormEpilogue(r, nw, 1e-6))
+    want_r = resid.double() + h.double() @ wd.double().T
+    assert torch.allclose(r.double(), want_r, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(rows.x.double(), want_r * nw.double(), atol=3e-2, rtol=2e-2)
+    assert torch.allclose(rows.ss.double().sum(0), (want_r ** 2).sum(1), rtol=1e-4)
+    assert rows.width == H and ops().gemm_tc_pair_error() == 0
+    # the rows it hands on are what the one-CTA kernel hands on for the rows that kernel takes
+    if M <= 64:
+        r1 = resid.clone()
+        one = ops().gemm_tc(h, wd, epilogue=AddNormEpilogue(r1, nw, 1e-6))
+        assert torch.allclose(r1, r, atol=1e-5, rtol=1e-5) and torch.allclose(one.x.float(), rows.x.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,K,qlens,norm,write,table", [(4, 2, 256, [70, 1, 50], True, True, True),
+                                                             (5, 1, 520, [33, 40], True, True, False),
+                                                             (2, 2, 128, [300], False, True, True),
+                                                             (8, 4, 1024, [3, 200, 90], True, False, True)])
+def test_gemm_tc_pair_qkv_rope_epilogue(monkeypatch, nq, nkv, K, qlens, norm, write, table):
+    """The paired kernel's q/k/v epilogue (more than 32 rows go to it): against the plain product
+    followed by the stand-alone kernel, with the cos/sin table and with angles computed in the epilogue;
+    seven heads (5 + 1 + 1) leave the second half of the last tile without a head."""
+    from acorninfer_b200.kernels.ops import RopeKvEpilogue
+    from tests.paged import rows_layout
+    torch.manual_seed(nq * 10 + nkv)
+    d, P, NP, eps, theta = 128, 16, 400, 3e-6, 1e4
+    befores = [0, 37, 4000][:len(qlens)]
+    lay = rows_layout(befores, qlens, P, NP, seed=2)
+    T = lay["num_tokens"]
+    assert T > 32
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+    qw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    inv = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    ref = torch.mm(x, w.t())
+    k_ref = torch.zeros(NP, nkv, P, d, device=DEV, dtype=torch.bfloat16)
+    v_ref = torch.zeros_like(k_ref)
+    ops().qk_rope_kv(ref, qw, kw, inv, lay["positions"], lay["token_row"], lay["block_table"], lay["page_base"],
+                     k_ref, v_ref, nq, nkv, d, d, False, eps)
+    k_pages, v_pages = torch.zeros_like(k_ref), torch.zeros_like(k_ref)
+    cos_sin = ops().rope_table(lay["positions"], inv) if table else None
+    if table:
+        ang = (lay["positions"].float()[:, None] * inv[None, :]).double()       # the angle itself is a float32 product
+        assert torch.allclose(cos_sin.double(), torch.cat([ang.cos(), ang.sin()], dim=1), atol=1e-6)
+    out = ops().gemm_tc_qkv_rope(x, w, RopeKvEpilogue(
+        lay["positions"], lay["token_row"], lay["block_table"], lay["page_base"], k_pages if write else None,
+        v_pages if write else None, qw, kw, inv, nq, nkv, eps, cos_sin=cos_sin))
+    assert ops().gemm_tc_pair_error() == 0
+    tol = dict(atol=4e-2, rtol=2e-2)
+    assert torch.allclose(out[:, :nq * d].float(), ref[:, :nq * d].float(), **tol)
+    if write:
+        assert torch.allclose(k_pages.float(), k_ref.float(), **tol)
+        assert torch.allclose(v_pages.float(), v_ref.float(), **tol)
+        assert float(k_pages.float().abs().sum()) > 0
+    else:
+        assert float(k_pages.float().abs().sum()) == 0 and float(v_pages.float().abs().sum()) == 0

@@ -39,7 +39,7 @@ def test_gemm_plans_are_valid_for_any_shape():
         if splits > 1:
             assert -(-K // 64) // splits >= 4        # every split keeps at least four steps of K
         if per_sm == 3:
-            assert M <= 32 and splits == 2
+            assert M <= 64 and splits == 2       # three short rings to an SM: tiles of up to 64 tokens
         if M > 64:
             assert per_sm == 2
 
@@ -51,3 +51,23 @@ def test_gemm_plans_of_the_decode_shapes():
     assert gemm_tc_plan(8, 24576, 4096) == (2, 3)    # 192 tiles on 148 SMs: half tiles, three CTAs to an SM
     assert gemm_tc_plan(8, 4096, 12288) == (8, 2)
     assert gemm_tc_plan(8, 151936, 4096) == (1, 2)
+
+
+def test_paired_kernel_is_asked_for_where_its_tiles_fill_the_device():
+    """256 x 256 tiles in rounds of one tile to a pair of SMs: 74 pairs on 148 SMs."""
+    from acorninfer_b200.kernels.ops import fused_rows_ok, pair_rows_ok
+    import torch
+    assert pair_rows_ok(2048, 4096)            # 128 tiles: two rounds, 0.86 full
+    assert not pair_rows_ok(1536, 4096)        # 96 tiles: two rounds, 0.65 full
+    assert not pair_rows_ok(200, 4096)         # below one tile of rows
+    assert pair_rows_ok(8192, 1024)            # a narrow model needs more rows: 128 tiles
+    assert not pair_rows_ok(2048, 1024)        # 32 tiles on 74 pairs
+    assert pair_rows_ok(2048, 4096, num_sms=64) == (128 / (4 * 32) >= 0.8)
+    # the one-CTA kernel's range is independent of the width; between the two ranges nothing is fused
+    assert fused_rows_ok(8, torch.bfloat16) and fused_rows_ok(32, torch.bfloat16, 4096)
+    assert not fused_rows_ok(33, torch.bfloat16, 4096) and not fused_rows_ok(1536, torch.bfloat16, 4096)
+    assert fused_rows_ok(2048, torch.bfloat16, 4096) and not fused_rows_ok(2048, torch.bfloat16)
+    # every product of the part has to fill the device: at 1,024 rows the q/k/v product of 6,144 columns does not
+    assert fused_rows_ok(1024, torch.bfloat16, 4096) and not fused_rows_ok(1024, torch.bfloat16, (6144, 4096))
+    assert fused_rows_ok(2048, torch.bfloat16, (6144, 4096)) and fused_rows_ok(2048, torch.bfloat16, (24576, 4096))
+    assert not fused_rows_ok(2048, torch.float32, 4096)

@@ -7,8 +7,9 @@ same, on the host for the plain model, which draws only what it needs (the token
 the ids in use; the output matrix in slabs).  The shapes are the ones the tiny configurations
 cannot reach: the gate/up product as 384 half tiles three to an SM, the down product split over a
 cluster at K = 12,288, the output matrix at N = 151,936, TMA decode attention with the splits the
-launch plan picks, tcgen05 prefill attention continuing inside a 128-key block, and above 32 rows
-the library products with the stand-alone norm / rotation / SwiGLU kernels.
+launch plan picks, tcgen05 prefill attention continuing inside a 128-key block, above 32 rows
+the library products with the stand-alone norm / rotation / SwiGLU kernels, and at 2,100 rows the
+paired tcgen05 product with its fused epilogues.
 
 Tolerances are measured (logits have a standard deviation of 1.3 and reach 6): the float32 engine
 differs from the float64 plain result by up to 3.7e-5 (sums over 12,288 terms; relative
@@ -135,6 +136,34 @@ def test_a_prompt_whole_and_in_portions(runner, plain64):
         at += n
     runner.close(rc)
     check(torch.cat(parts), want, dtype_of(runner), "portions 200 + 60 + 40")
+
+
+_LONG = {}
+
+
+def test_a_long_prompt_on_the_paired_kernel(runner, plain64):
+    """2,100 tokens in one step: in bfloat16 every product of the layers runs on the paired tcgen05 kernel
+    (nine token tiles: the last one holds 52 tokens) with q/k norm, rotation and the cache write, SwiGLU
+    and the residual sums with the next norm's sums as its epilogues; in float32 on the tiled CUDA-core
+    product.  Places at the edges of the 256-token tiles and of the 128-key attention blocks."""
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.kernels import ops
+    ids = random_tokens(2100, runner.vocab_size, 43)
+    places = [0, 1, 127, 128, 255, 256, 1023, 1024, 2047, 2048, 2099]
+    if "want" not in _LONG:
+        _LONG["want"] = plain64.logits(ids, places)
+    before = dict(ops.COUNTS)
+    rc = runner.open("long")
+    got = runner.step([StepEntry(rc, ids, places)])
+    runner.close(rc)
+    ran = {k: v - before.get(k, 0) for k, v in ops.COUNTS.items() if v - before.get(k, 0)}
+    if runner.dtype == torch.bfloat16:
+        # the last layer's down product has no norm after it for all rows (the final norm takes the wanted
+        # rows only): it adds to the residual stream through the library product's C operand
+        assert ran.get("gemm_tc_pair") == 3 * LAYERS - 1 and ran.get("gemm_tc_pair_qkv_rope") == LAYERS
+        assert "swiglu" not in ran and "qk_rope_kv" not in ran
+        ops.raise_on_kernel_error()
+    check(got, _LONG["want"], dtype_of(runner), "2,100 tokens whole")
 
 
 def decode_case(runner, side, rows, prompt_lens, steps, seed):

@@ -197,3 +197,30 @@ def test_weights_stored_in_float32_stay_float32_under_a_bfloat16_engine(tmp_path
     got = traces.collect(TraceSession(runner).step, steps)
     for (rid, pos), row in got.items():
         assert np.abs(row - ref[rid][pos]).max() < 2e-2, (rid, pos)
+
+
+@pytest.mark.parametrize("cut", ["whole", "mixed_long"])
+def test_paired_kernel_path_matches_plain(monkeypatch, tmp_path, cut):
+    """Steps of more than 32 rows on the paired tcgen05 kernel with its fused epilogues (which the engine
+    takes by itself only where its tiles fill the device: thousands of rows at real widths): forced here
+    for every such step of the head-size-128 configuration, whole prompts and long portions beside
+    decoded tokens, against the plain model."""
+    from acorninfer_b200.kernels import ops
+    from tests.tiny import TINY_D
+    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_ROWS", 33)
+    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL", 0.0)
+    tiny = TINY_D
+    d = make_model_dir(tmp_path, tiny)
+    w = read_weights(d)
+    lengths = [40, 157, 70, 33, 300, 64]
+    reqs = {f"r{i}": random_tokens(n, tiny["cfg"].vocab_size, 2000 + i) for i, n in enumerate(lengths)}
+    ref = {rid: plain.forward(sizes_of(tiny["cfg"]), w, toks).numpy() for rid, toks in reqs.items()}
+    steps = traces.whole(reqs) if cut == "whole" else traces.mixed(reqs, max_portion=60, min_portion=34, stagger=2)
+    before = dict(ops.COUNTS)
+    got = run_cut(tiny, d, steps, "bfloat16")
+    ran = {k: v - before.get(k, 0) for k, v in ops.COUNTS.items()}
+    assert ran.get("gemm_tc_pair", 0) > 0 and ran.get("gemm_tc_pair_qkv_rope", 0) > 0 and ran.get("rope_table", 0) > 0
+    assert len(got) == sum(lengths)
+    for (rid, pos), row in got.items():
+        diff = np.abs(row - ref[rid][pos]).max()
+        assert diff < TOL["bfloat16"], f"{cut}: request {rid} position {pos}: |d|={diff:.3e}"
