@@ -58,6 +58,15 @@ def bench_gemm(a) -> None:
     if a.normed:       # x arrives as rows that lack their RMS factor (32 partial sums a row)
         xin = ops.NormedRows(x, torch.rand(32, a.m, device=DEV) + 1.0, 1e-6, a.k)
     ep = ops.AddNormEpilogue(resid, norm_w, 1e-6) if a.epilogue == "add_norm" else None
+    if a.kernel == "pair":
+        us = _time([lambda w=w: ops.gemm_tc_pair(xin, w, torch.bfloat16, epilogue=ep, swiglu=a.epilogue == "swiglu")
+                    for w in ws], a.reps, a.graph)
+        lib = _time([lambda w=w: torch.mm(x, w.t()) for w in ws], a.reps, a.graph) if a.library else float("nan")
+        fl = 2.0 * a.m * a.n * a.k
+        print(f"gemm_tcgen05_pair M={a.m} N={a.n} K={a.k} epilogue={a.epilogue} normed={a.normed}: {us:.1f} us, "
+              f"{fl / us / 1e6:.1f} TFLOPS; library product {lib:.1f} us, {fl / lib / 1e6:.1f} TFLOPS; "
+              f"error flag {ops.gemm_tc_pair_error()}")
+        return
     us = _time([lambda w=w: ops.gemm_tc(xin, w, torch.bfloat16, splits=splits, epilogue=ep,
                                         swiglu=a.epilogue == "swiglu", per_sm=per_sm) for w in ws], a.reps, a.graph)
     lib = _time([lambda w=w: torch.mm(x, w.t()) for w in ws], a.reps, a.graph) if a.library else float("nan")
@@ -172,6 +181,8 @@ def main(argv=None) -> int:
     g.add_argument("--splits", type=int, default=0)
     g.add_argument("--per-sm", type=int, default=2, help="with --splits: CTAs to an SM (2: deep ring, 3: short ring)")
     g.add_argument("--library", type=int, default=1, help="also time the library product")
+    g.add_argument("--kernel", default="one", choices=["one", "pair"],
+                   help="one: the one-CTA kernel (few rows); pair: the paired kernel (many rows)")
     g.add_argument("--epilogue", default="none", choices=["none", "add_norm", "swiglu"])
     g.add_argument("--normed", type=int, default=0, help="1: x is NormedRows (row factors applied in the epilogue)")
     for name in ("attn-decode", "attn-prefill"):
