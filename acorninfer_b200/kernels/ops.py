@@ -624,6 +624,7 @@ GEMM_TC_MAX_ROWS = 32
 # The paired kernel (256 x 256 tiles, a pair of SMs to a tile at a time, fused epilogues) is used from
 # this many rows on, where its tiles fill the device: see ``pair_rows_ok``.
 GEMM_PAIR_MIN_ROWS = 256
+GEMM_PAIR_MAX_ROWS = 6144
 GEMM_PAIR_MIN_FILL = 0.8
 
 
@@ -631,8 +632,10 @@ def pair_rows_ok(num_rows: int, width: int, num_sms: int = 148) -> bool:
     """Whether a product of ``num_rows`` rows and ``width`` output columns suits the paired kernel: its
     tiles of 256 x 256 are taken in rounds of one tile to a pair of SMs, and the rounds must be filled to
     ``GEMM_PAIR_MIN_FILL`` on average (128 tiles on 74 pairs: two rounds, 0.86; 96 tiles: two rounds,
-    0.65, where the library's choice of tile shapes is faster)."""
-    if num_rows < GEMM_PAIR_MIN_ROWS:
+    0.65, where the library's choice of tile shapes is faster).  Steps of more than ``GEMM_PAIR_MAX_ROWS``
+    rows run so long under the power cap that the library's kernel, which moves half the bytes from L2
+    (multicast loads), keeps the higher clock and wins by 3 to 5 % (measured at 8,192 rows)."""
+    if num_rows < GEMM_PAIR_MIN_ROWS or num_rows > GEMM_PAIR_MAX_ROWS:
         return False
     pairs = max(num_sms // 2, 1)
     tiles = -(-num_rows // 256) * -(-width // 256)
