@@ -79,21 +79,6 @@ struct G2Params {
     float rope_eps;
 };
 
-// A wait bounded in time (two seconds: no wait of this kernel is longer than the kernel before it runs);
-// false when it gave up.
-__device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity) {
-    long long t0 = 0;
-    for (uint32_t tries = 0;; ++tries) {
-        if (mbar_test(bar, parity)) return true;
-        if ((tries & 1023u) == 1023u) {
-            long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ll) return false;
-        }
-    }
-}
-
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -203,7 +188,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
             const int x_row = tm * 2 * G2_BT + (int)rank * G2_BT, w_row = tn * 2 * G2_BW + (int)rank * G2_BW;
             for (int kb = 0; kb < p.kblocks; ++kb, ++g) {
                 const int s = g % G2_STAGES;
-                bool got = mbar_wait_timed(empty0 + 8 * s, ((g / G2_STAGES) & 1) ^ 1);
+                bool got = mbar_wait(empty0 + 8 * s, ((g / G2_STAGES) & 1) ^ 1);
                 if (!got && lane == 0) tc_fail(&g_gemm_pair_error, 1, ACORN_KERNEL_GEMM_PAIR);
                 good = __all_sync(0xffffffffu, got);
                 if (!good) break;
@@ -225,7 +210,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
             bool good = true;
             for (int tile = pair; tile < tiles && good; tile += pairs, ++i) {
                 const int as = i & 1;
-                bool got = mbar_wait_timed(acc_free0 + 8 * as, ((i >> 1) & 1) ^ 1);      // both CTAs have read this accumulator
+                bool got = mbar_wait(acc_free0 + 8 * as, ((i >> 1) & 1) ^ 1);      // both CTAs have read this accumulator
                 if (!got && lane == 0) tc_fail(&g_gemm_pair_error, 2, ACORN_KERNEL_GEMM_PAIR);
                 good = __all_sync(0xffffffffu, got);
                 if (!good) break;
@@ -233,7 +218,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
                 const uint32_t d = tmem_base + (uint32_t)(as * G2_ACC_COLS);
                 for (int kb = 0; kb < p.kblocks; ++kb, ++g) {
                     const int s = g % G2_STAGES;
-                    got = mbar_wait_timed(full0 + 8 * s, (g / G2_STAGES) & 1);
+                    got = mbar_wait(full0 + 8 * s, (g / G2_STAGES) & 1);
                     if (!got && lane == 0) tc_fail(&g_gemm_pair_error, 3, ACORN_KERNEL_GEMM_PAIR);
                     good = __all_sync(0xffffffffu, got);
                     if (!good) break;
@@ -269,7 +254,7 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
                 for (int q = 0; q < p.ss_parts; ++q) tot += p.ss_in[(int64_t)q * p.M + m];
                 inv = rsqrtf(tot / (float)p.norm_width + p.eps);
             }
-            bool got = mbar_wait_timed(acc_full0 + 8 * as, (i >> 1) & 1);
+            bool got = mbar_wait(acc_full0 + 8 * as, (i >> 1) & 1);
             if (!got && lane == 0) tc_fail(&g_gemm_pair_error, 4, ACORN_KERNEL_GEMM_PAIR);
             good = __all_sync(0xffffffffu, got);
             if (!good) break;

@@ -6,7 +6,6 @@
 
 #include "common.cuh"
 
-#define TC_WAIT_LIMIT (1u << 22)
 
 // A kernel whose bounded wait gives up records where in its own flag and in a word of pinned,
 // device-mapped host memory, which the host reads without a CUDA call (so it can look after
@@ -56,16 +55,25 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
 }
 
-// Bounded wait for the phase with the given parity; false when it gave up.
+// Bounded wait for the phase with the given parity; false when it gave up.  The bound is time (two
+// seconds by the global timer, looked at every 1,024 tries: no wait of these kernels is longer than the
+// kernel before them runs), so that a kernel whose hand-over is broken ends soon whatever a try costs.
+#define TC_WAIT_NS 2000000000ll
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t tries = 0; tries < TC_WAIT_LIMIT; ++tries) {
+    long long t0 = 0;
+    for (uint32_t tries = 0;; ++tries) {
         uint32_t ok;
         asm volatile(
             "{\n .reg .pred P1;\n mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n selp.u32 %0, 1, 0, P1;\n}\n"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
+        if ((tries & 1023u) == 1023u) {
+            long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > TC_WAIT_NS) return false;
+        }
     }
-    return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
