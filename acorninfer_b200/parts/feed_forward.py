@@ -49,9 +49,16 @@ class SwiGLU(FeedForward):
                 and self.w_down.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.intermediate_size % 8 == 0)
 
+    def _gate_up_fuses(self, num_rows):
+        """The gate/up product alone on the paired kernel with SwiGLU as its epilogue: it is the widest
+        product of a layer, so its tiles fill the device from far fewer rows than the whole layer needs
+        (512 rows at Qwen3-8B widths), and the stand-alone SwiGLU kernel with its round trip is spared."""
+        return (self.ctx.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+                and ops.pair_rows_ok(num_rows, 2 * self.intermediate_size, ops.device_sms(self.ctx.device)))
+
     def forward(self, x, inputs, epilogue=None, residual32=None):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]
-        if self.block == 64 and self.fusable(rows):
+        if self.block == 64 and (self.fusable(rows) or self._gate_up_fuses(rows)):
             h = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype, swiglu=True)
         else:
             gu = ops.linear(x, self.w_gate_up, out_dtype=self.ctx.dtype)

@@ -112,6 +112,26 @@ def test_feed_forward_part(dtype):
     assert torch.allclose(ff.forward(x.to(DEV), None).double().cpu(), plain.swiglu_mlp(x.double(), w, "p."), **TOL[dtype])
 
 
+def test_feed_forward_part_with_only_its_gate_up_product_on_the_paired_kernel(monkeypatch):
+    """Between the few rows of the one-CTA kernel and the many of a wholly fused layer, the gate/up
+    product alone may run on the paired kernel with SwiGLU as its epilogue (its tiles fill the device
+    first); forced here for 40 rows of a small part, the down product on the library."""
+    from acorninfer_b200.kernels import ops
+    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_ROWS", 33)
+    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL", 0.0)
+    monkeypatch.setattr(ops, "fused_rows_ok", lambda rows, dtype, widths=None, num_sms=148: dtype == torch.bfloat16 and rows <= 32)
+    ctx = context(torch.bfloat16)
+    hidden, inter = 96, 192                          # intermediate size a multiple of 64: blocks of gate and up rows
+    ff = build_part(FEED_FORWARDS, PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter}), ctx)
+    w = {"p." + k: v for k, v in random_bind(ff, torch.bfloat16, 5).items()}
+    x = torch.randn(40, hidden).to(torch.bfloat16)
+    before = dict(ops.COUNTS)
+    got = ff.forward(x.to(DEV), None)
+    ran = {k: v - before.get(k, 0) for k, v in ops.COUNTS.items() if v - before.get(k, 0)}
+    assert ran.get("gemm_tc_pair") == 1 and "swiglu" not in ran
+    assert torch.allclose(got.double().cpu(), plain.swiglu_mlp(x.double(), w, "p."), **TOL[torch.bfloat16])
+
+
 @pytest.mark.parametrize("pairing,rot", [("half", 48), ("interleaved", 32)])
 def test_position_encoding_part_constants(pairing, rot):
     ctx = context(torch.float32)
