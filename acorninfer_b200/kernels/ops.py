@@ -625,21 +625,30 @@ GEMM_TC_MAX_ROWS = 32
 # this many rows on, where its tiles fill the device: see ``pair_rows_ok``.
 GEMM_PAIR_MIN_ROWS = 256
 GEMM_PAIR_MAX_ROWS = 6144
-GEMM_PAIR_MIN_FILL = 0.8
+GEMM_PAIR_MIN_FILL = 0.8          # for every product of a layer, when the whole layer is fused
+GEMM_PAIR_MIN_FILL_ALONE = 0.6    # for the widest product taken alone (gate/up with SwiGLU) ...
+GEMM_PAIR_ALONE_MIN_K = 2048      # ... whose K must be long enough for a tile's k-steps to hide its epilogue
 
 
-def pair_rows_ok(num_rows: int, width: int, num_sms: int = 148) -> bool:
-    """Whether a product of ``num_rows`` rows and ``width`` output columns suits the paired kernel: its
-    tiles of 256 x 256 are taken in rounds of one tile to a pair of SMs, and the rounds must be filled to
-    ``GEMM_PAIR_MIN_FILL`` on average (128 tiles on 74 pairs: two rounds, 0.86; 96 tiles: two rounds,
-    0.65, where the library's choice of tile shapes is faster).  Steps of more than ``GEMM_PAIR_MAX_ROWS``
-    rows run so long under the power cap that the library's kernel, which moves half the bytes from L2
-    (multicast loads), keeps the higher clock and wins by 3 to 5 % (measured at 8,192 rows)."""
-    if num_rows < GEMM_PAIR_MIN_ROWS or num_rows > GEMM_PAIR_MAX_ROWS:
-        return False
+def pair_fill(num_rows: int, width: int, num_sms: int = 148) -> float:
+    """How full the paired kernel's rounds are for a product of ``num_rows`` rows and ``width`` output
+    columns: its tiles of 256 x 256 are taken in rounds of one tile to a pair of SMs; the product's
+    elements over those the rounds could hold (128 full tiles on 74 pairs: two rounds, 0.86; 96 tiles:
+    two rounds, 0.65; 257 rows: every second tile holds one row)."""
     pairs = max(num_sms // 2, 1)
     tiles = -(-num_rows // 256) * -(-width // 256)
-    return tiles / (-(-tiles // pairs) * pairs) >= GEMM_PAIR_MIN_FILL
+    return num_rows * width / (-(-tiles // pairs) * pairs * 65536)
+
+
+def pair_rows_ok(num_rows: int, width: int, num_sms: int = 148, min_fill: float | None = None) -> bool:
+    """Whether a product of ``num_rows`` rows and ``width`` output columns suits the paired kernel: its
+    rounds must be filled to ``min_fill`` (``GEMM_PAIR_MIN_FILL`` if not given); below that the library's
+    choice of tile shapes is faster.  Steps of more than ``GEMM_PAIR_MAX_ROWS`` rows run so long under
+    the power cap that the library's kernel, which moves half the bytes from L2 (multicast loads), keeps
+    the higher clock and wins by 3 to 5 % (measured at 8,192 rows)."""
+    if num_rows < GEMM_PAIR_MIN_ROWS or num_rows > GEMM_PAIR_MAX_ROWS:
+        return False
+    return pair_fill(num_rows, width, num_sms) >= (GEMM_PAIR_MIN_FILL if min_fill is None else min_fill)
 
 
 @dataclass

@@ -52,9 +52,14 @@ class SwiGLU(FeedForward):
     def _gate_up_fuses(self, num_rows):
         """The gate/up product alone on the paired kernel with SwiGLU as its epilogue: it is the widest
         product of a layer, so its tiles fill the device from far fewer rows than the whole layer needs
-        (512 rows at Qwen3-8B widths), and the stand-alone SwiGLU kernel with its round trip is spared."""
+        (about 360 rows at Qwen3-8B widths), and the stand-alone SwiGLU kernel with its round trip is
+        spared.  Measured: a gain from 384 rows on at hidden size 4,096 (a loss at 300 rows, where the
+        second token tile is nearly empty); none at hidden size 1,024, where a tile's 16 k-steps are too
+        few to hide its epilogue."""
         return (self.ctx.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
-                and ops.pair_rows_ok(num_rows, 2 * self.intermediate_size, ops.device_sms(self.ctx.device)))
+                and self.hidden_size >= ops.GEMM_PAIR_ALONE_MIN_K
+                and ops.pair_rows_ok(num_rows, 2 * self.intermediate_size, ops.device_sms(self.ctx.device),
+                                     ops.GEMM_PAIR_MIN_FILL_ALONE))
 
     def forward(self, x, inputs, epilogue=None, residual32=None):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]

@@ -118,7 +118,8 @@ def test_feed_forward_part_with_only_its_gate_up_product_on_the_paired_kernel(mo
     first); forced here for 40 rows of a small part, the down product on the library."""
     from acorninfer_b200.kernels import ops
     monkeypatch.setattr(ops, "GEMM_PAIR_MIN_ROWS", 33)
-    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL", 0.0)
+    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL_ALONE", 0.0)
+    monkeypatch.setattr(ops, "GEMM_PAIR_ALONE_MIN_K", 0)
     monkeypatch.setattr(ops, "fused_rows_ok", lambda rows, dtype, widths=None, num_sms=148: dtype == torch.bfloat16 and rows <= 32)
     ctx = context(torch.bfloat16)
     hidden, inter = 96, 192                          # intermediate size a multiple of 64: blocks of gate and up rows

@@ -209,6 +209,8 @@ def test_paired_kernel_path_matches_plain(monkeypatch, tmp_path, cut):
     from tests.tiny import TINY_D
     monkeypatch.setattr(ops, "GEMM_PAIR_MIN_ROWS", 33)
     monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL", 0.0)
+    monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL_ALONE", 0.0)
+    monkeypatch.setattr(ops, "GEMM_PAIR_ALONE_MIN_K", 0)
     tiny = TINY_D
     d = make_model_dir(tmp_path, tiny)
     w = read_weights(d)
