@@ -102,7 +102,7 @@ class ModelRunner:
     def close(self, cache: RequestCache) -> None:
         self.manager.close(cache)
 
-    def warm_up(self, prompt_tokens: tuple[int, ...] = (16, 128, 512, 2048, 8192),
+    def warm_up(self, prompt_tokens: tuple[int, ...] = (16, 64, 128, 256, 512, 1024, 2048, 4096, 8192),
                 decode_rows: tuple[int, ...] = (1, 2, 4, 8)) -> None:
         """Runs throw-away steps so that what a first request would pay for is paid at load: the
         library's kernels for prompt portions of several sizes (it loads them when first used) and
