@@ -248,3 +248,18 @@ def test_gemm_tc_pair_qkv_rope_epilogue(monkeypatch, nq, nkv, K, qlens, norm, wr
         assert float(k_pages.float().abs().sum()) > 0
     else:
         assert float(k_pages.float().abs().sum()) == 0 and float(v_pages.float().abs().sum()) == 0
+
+
+def test_gemm_tc_pair_random_shapes():
+    """Thirty random shapes (rows 1 .. 3,000, widths that are no multiple of the tile, K in steps of 8)
+    against the library product of the same bfloat16 operands, with every number of pairs from few to all."""
+    import random
+    rng = random.Random(7)
+    for _ in range(30):
+        M, N, K = rng.randint(1, 3000), 8 * rng.randint(1, 600), 8 * rng.randint(1, 300)
+        x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=DEV) / K ** 0.5).to(torch.bfloat16)
+        out = ops().gemm_tc_pair(x, w, torch.float32, pairs=rng.choice([None, 1, 3, 37]))
+        want = torch.mm(x, w.t(), out_dtype=torch.float32)
+        assert torch.allclose(out, want, atol=2e-3, rtol=2e-3), (M, N, K)
+    assert ops().gemm_tc_pair_error() == 0
