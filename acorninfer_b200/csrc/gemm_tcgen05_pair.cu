@@ -1,4 +1,4 @@
-// out[M, N] = x[M, K] * W[N, K]^T in bfloat16 for many rows (prompts, large decode batches): tcgen05
+// out[M, N] = x[M, K] * W[N, K]^T in bfloat16 for many rows (steps of hundreds to thousands of tokens): tcgen05
 // tensor cores driven by pairs of CTAs on neighbouring SMs (cta_group::2), persistent, warp-specialised.
 //
 // A pair owns a tile of 256 tokens by 256 rows of W.  Each CTA of the pair loads its own half of both
@@ -358,9 +358,8 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm_tcgen05_pair_kernel(const 
                         page = p.block_table[(int64_t)r * p.table_stride + (pos >> p.logP) - p.page_base[r]];
                     }
                 }
-                for (int hh = half; hh == half; ++hh) {
-                    const int head = tn * 2 + hh;
-                    if (head >= heads) break;
+                const int hh = half, head = tn * 2 + hh;         // this warp's head of the tile's two
+                if (head < heads) {
                     const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
                     const int kvh = is_q ? 0 : (head - p.nq) % p.nkv;
                     const float* hw = is_q ? p.q_w : is_k ? p.k_w : nullptr;
