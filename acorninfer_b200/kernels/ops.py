@@ -624,9 +624,10 @@ GEMM_TC_MAX_ROWS = 32
 # The paired kernel (256 x 256 tiles, a pair of SMs to a tile at a time, fused epilogues) is used from
 # this many rows on, where its tiles fill the device: see ``pair_rows_ok``.
 GEMM_PAIR_MIN_ROWS = 256
-GEMM_PAIR_MAX_ROWS = 6144
+GEMM_PAIR_MAX_ROWS = 3072
 GEMM_PAIR_MIN_FILL = 0.8          # for every product of a layer, when the whole layer is fused
 GEMM_PAIR_MIN_FILL_ALONE = 0.6    # for the widest product taken alone (gate/up with SwiGLU) ...
+GEMM_PAIR_ALONE_MAX_ROWS = 8192
 GEMM_PAIR_ALONE_MIN_K = 2048      # ... whose K must be long enough for a tile's k-steps to hide its epilogue
 
 
@@ -640,13 +641,17 @@ def pair_fill(num_rows: int, width: int, num_sms: int = 148) -> float:
     return num_rows * width / (-(-tiles // pairs) * pairs * 65536)
 
 
-def pair_rows_ok(num_rows: int, width: int, num_sms: int = 148, min_fill: float | None = None) -> bool:
+def pair_rows_ok(num_rows: int, width: int, num_sms: int = 148, min_fill: float | None = None,
+                 max_rows: int | None = None) -> bool:
     """Whether a product of ``num_rows`` rows and ``width`` output columns suits the paired kernel: its
     rounds must be filled to ``min_fill`` (``GEMM_PAIR_MIN_FILL`` if not given); below that the library's
-    choice of tile shapes is faster.  Steps of more than ``GEMM_PAIR_MAX_ROWS`` rows run so long under
-    the power cap that the library's kernel, which moves half the bytes from L2 (multicast loads), keeps
-    the higher clock and wins by 3 to 5 % (measured at 8,192 rows)."""
-    if num_rows < GEMM_PAIR_MIN_ROWS or num_rows > GEMM_PAIR_MAX_ROWS:
+    choice of tile shapes is faster.  Steps of more than ``max_rows`` rows (``GEMM_PAIR_MAX_ROWS`` if not
+    given) run so long under the power cap that the library's kernel, which moves half the bytes from L2
+    (multicast loads), keeps the higher clock: with every product of the layers on the paired kernel a step
+    of 4,096 rows took 53.3 ms against 51.8 ms with the gate/up product alone on it, one of 6,144 rows 84.2
+    against 80.9 (54.7 and 84.3 on the library alone); the gate/up product alone stops paying at about
+    12,000 rows."""
+    if num_rows < GEMM_PAIR_MIN_ROWS or num_rows > (GEMM_PAIR_MAX_ROWS if max_rows is None else max_rows):
         return False
     return pair_fill(num_rows, width, num_sms) >= (GEMM_PAIR_MIN_FILL if min_fill is None else min_fill)
 

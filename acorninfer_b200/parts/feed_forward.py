@@ -59,7 +59,7 @@ class SwiGLU(FeedForward):
         return (self.ctx.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
                 and self.hidden_size >= ops.GEMM_PAIR_ALONE_MIN_K
                 and ops.pair_rows_ok(num_rows, 2 * self.intermediate_size, ops.device_sms(self.ctx.device),
-                                     ops.GEMM_PAIR_MIN_FILL_ALONE))
+                                     ops.GEMM_PAIR_MIN_FILL_ALONE, ops.GEMM_PAIR_ALONE_MAX_ROWS))
 
     def forward(self, x, inputs, epilogue=None, residual32=None):
         rows = x.x.shape[0] if isinstance(x, ops.NormedRows) else x.shape[0]

@@ -60,12 +60,13 @@ def test_paired_kernel_is_asked_for_where_its_tiles_fill_the_device():
     assert pair_rows_ok(2048, 4096)            # 128 tiles: two rounds, 0.86 full
     assert not pair_rows_ok(1536, 4096)        # 96 tiles: two rounds, 0.65 full
     assert not pair_rows_ok(200, 4096)         # below one tile of rows
-    assert not pair_rows_ok(6144, 1024) and pair_rows_ok(4608, 1024)    # a narrow model needs more rows: 96 tiles on 148 places, 72 on 74
+    assert not pair_rows_ok(2048, 1024, max_rows=8192) and pair_rows_ok(4608, 1024, max_rows=8192)    # a narrow model needs more rows: 32 tiles, 72 tiles on 74 pairs
     assert not pair_rows_ok(1800, 4096)        # eight token tiles, the last one a fifth full: 0.76
     # the widest product taken alone needs less: gate/up of 24,576 columns from about 360 rows on
     assert pair_rows_ok(384, 24576, min_fill=0.6) and not pair_rows_ok(300, 24576, min_fill=0.6)
     assert not pair_rows_ok(257, 24576, min_fill=0.6)     # the second token tile holds one row
-    assert not pair_rows_ok(8192, 4096)        # the longest steps stay on the library (the power cap)
+    assert pair_rows_ok(3072, 4096) and not pair_rows_ok(4096, 4096)       # the longest steps: not every product (the power cap)
+    assert pair_rows_ok(4096, 24576, min_fill=0.6, max_rows=8192) and not pair_rows_ok(12288, 24576, min_fill=0.6, max_rows=8192)
     assert not pair_rows_ok(2048, 1024)        # 32 tiles on 74 pairs
     assert pair_rows_ok(2048, 4096, num_sms=64) == (128 / (4 * 32) >= 0.8)
     # the one-CTA kernel's range is independent of the width; between the two ranges nothing is fused
