@@ -199,19 +199,21 @@ def test_weights_stored_in_float32_stay_float32_under_a_bfloat16_engine(tmp_path
         assert np.abs(row - ref[rid][pos]).max() < 2e-2, (rid, pos)
 
 
+@pytest.mark.parametrize("which", ["tiny_d", "tiny_c"])
 @pytest.mark.parametrize("cut", ["whole", "mixed_long"])
-def test_paired_kernel_path_matches_plain(monkeypatch, tmp_path, cut):
+def test_paired_kernel_path_matches_plain(monkeypatch, tmp_path, cut, which):
     """Steps of more than 32 rows on the paired tcgen05 kernel with its fused epilogues (which the engine
     takes by itself only where its tiles fill the device: thousands of rows at real widths): forced here
     for every such step of the head-size-128 configuration, whole prompts and long portions beside
-    decoded tokens, against the plain model."""
+    decoded tokens, against the plain model.  The configuration with head size 48 and a feed-forward
+    width that is no multiple of 64 takes the kernel's plain form fed with un-normalised rows, followed
+    by the stand-alone rotation and SwiGLU kernels."""
     from acorninfer_b200.kernels import ops
-    from tests.tiny import TINY_D
     monkeypatch.setattr(ops, "GEMM_PAIR_MIN_ROWS", 33)
     monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL", 0.0)
     monkeypatch.setattr(ops, "GEMM_PAIR_MIN_FILL_ALONE", 0.0)
     monkeypatch.setattr(ops, "GEMM_PAIR_ALONE_MIN_K", 0)
-    tiny = TINY_D
+    tiny = TINIES[which]
     d = make_model_dir(tmp_path, tiny)
     w = read_weights(d)
     lengths = [40, 157, 70, 33, 300, 64]
@@ -221,7 +223,11 @@ def test_paired_kernel_path_matches_plain(monkeypatch, tmp_path, cut):
     before = dict(ops.COUNTS)
     got = run_cut(tiny, d, steps, "bfloat16")
     ran = {k: v - before.get(k, 0) for k, v in ops.COUNTS.items()}
-    assert ran.get("gemm_tc_pair", 0) > 0 and ran.get("gemm_tc_pair_qkv_rope", 0) > 0 and ran.get("rope_table", 0) > 0
+    assert ran.get("gemm_tc_pair", 0) > 0
+    if which == "tiny_d":
+        assert ran.get("gemm_tc_pair_qkv_rope", 0) > 0 and ran.get("rope_table", 0) > 0 and not ran.get("swiglu", 0)
+    else:
+        assert ran.get("qk_rope_kv", 0) > 0 and ran.get("swiglu", 0) > 0 and not ran.get("gemm_tc_pair_qkv_rope", 0)
     assert len(got) == sum(lengths)
     for (rid, pos), row in got.items():
         diff = np.abs(row - ref[rid][pos]).max()
