@@ -8,8 +8,9 @@ the ids in use; the output matrix in slabs).  The shapes are the ones the tiny c
 cannot reach: the gate/up product as 384 half tiles three to an SM, the down product split over a
 cluster at K = 12,288, the output matrix at N = 151,936, TMA decode attention with the splits the
 launch plan picks, tcgen05 prefill attention continuing inside a 128-key block, above 32 rows
-the library products with the stand-alone norm / rotation / SwiGLU kernels, and at 2,100 rows the
-paired tcgen05 product with its fused epilogues.
+the library products with the stand-alone norm / rotation / SwiGLU kernels, at 600 rows the gate/up
+product alone on the paired tcgen05 kernel, and at 2,100 rows every product of a layer on it with its
+fused epilogues.
 
 Tolerances are measured (logits have a standard deviation of 1.3 and reach 6): the float32 engine
 differs from the float64 plain result by up to 3.7e-5 (sums over 12,288 terms; relative
@@ -164,6 +165,27 @@ def test_a_long_prompt_on_the_paired_kernel(runner, plain64):
         assert "swiglu" not in ran and "qk_rope_kv" not in ran
         ops.raise_on_kernel_error()
     check(got, _LONG["want"], dtype_of(runner), "2,100 tokens whole")
+
+
+def test_a_prompt_of_600_tokens_with_gate_up_alone_on_the_paired_kernel(runner, plain64):
+    """600 tokens in one step: too few for every product of a layer to fill the device, enough for the
+    gate/up product, which in bfloat16 runs on the paired kernel with SwiGLU while the others stay on the
+    library (three token tiles, the last one holding 88 tokens)."""
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.kernels import ops
+    ids = random_tokens(600, runner.vocab_size, 47)
+    places = [0, 255, 256, 511, 512, 599]
+    want = plain64.logits(ids, places)
+    before = dict(ops.COUNTS)
+    rc = runner.open("mid")
+    got = runner.step([StepEntry(rc, ids, places)])
+    runner.close(rc)
+    ran = {k: v - before.get(k, 0) for k, v in ops.COUNTS.items() if v - before.get(k, 0)}
+    if runner.dtype == torch.bfloat16:
+        assert ran.get("gemm_tc_pair") == LAYERS and "gemm_tc_pair_qkv_rope" not in ran and "swiglu" not in ran
+        assert ran.get("qk_rope_kv") == LAYERS
+        ops.raise_on_kernel_error()
+    check(got, want, dtype_of(runner), "600 tokens whole")
 
 
 def decode_case(runner, side, rows, prompt_lens, steps, seed):
