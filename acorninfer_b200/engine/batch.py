@@ -206,6 +206,50 @@ def pad_decode_plan(plan: StepPlan, pad_pages: list[int], pad_slot: int, builder
     return padded
 
 
+# A prompt portion that is a step of its own is padded to a multiple of this many tokens (up to the
+# limit), so that a few captured graphs serve every length.
+PREFILL_BUCKET = 32
+PREFILL_GRAPH_MAX_TOKENS = 512
+
+
+def prefill_bucket(n: int) -> int:
+    return -(-n // PREFILL_BUCKET) * PREFILL_BUCKET
+
+
+def pad_prefill_plan(plan: StepPlan, pad_pages: list[int], page_size: int, builders: dict | None = None) -> StepPlan:
+    """A step of one row of several tokens, padded to its bucket: the added tokens (id 0) continue the
+    row at the positions after its last token.  Their keys and values fall either into the slots of the
+    row's last page that lie beyond its length (the request's next tokens overwrite them before anything
+    reads them) or, past the pages the row holds, into the manager's padding page, which the added table
+    entries name.  Causal attention keeps them out of every real token's result; callers use the logits of
+    the wanted places only, which do not move.  The parts' arrays are built again for the padded plan."""
+    T = plan.num_tokens
+    Tb = prefill_bucket(T)
+    if plan.num_rows != 1 or Tb == T:
+        return plan
+    extra = Tb - T
+    i32 = np.int32
+    start = int(plan.row_pos[0])
+    groups = []
+    for g, pad_page in zip(plan.groups, pad_pages):
+        kv_len = (g.kv_len + extra).astype(i32)
+        base = int(g.page_base[0])
+        need = -(-int(kv_len[0]) // page_size) - base             # table entries the padded row reads and writes
+        have = -(-(start + T) // page_size) - base                # entries that name pages the row holds
+        stride = max(g.block_table.shape[1], _table_stride(need))
+        bt = np.zeros((1, stride), i32)
+        bt[0, :g.block_table.shape[1]] = g.block_table[0]
+        bt[0, have:need] = pad_page
+        groups.append(GroupPlan(kv_len, g.page_base, bt, int(kv_len[0])))
+    padded = StepPlan(
+        Tb, 1, np.concatenate([plan.token_ids, np.zeros(extra, i32)]),
+        np.concatenate([plan.positions, np.arange(start + T, start + Tb, dtype=i32)]),
+        np.zeros(Tb, i32), np.asarray([0, Tb], i32), plan.row_pos, plan.row_slot, plan.logit_tokens, groups,
+        [Tb], Tb, False, plan.patch_dst, plan.patch_src)
+    padded.extra = build_extra(padded, builders)
+    return padded
+
+
 # --------------------------------------------------------------------------- device side
 
 

@@ -31,7 +31,8 @@ from ..models.decoder import Decoder
 from ..registry import load_config, spec_for
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_state
-from .batch import BatchError, StepEntry, StepWorkspace, pad_decode_plan, plan_step, validate_entries
+from .batch import (PREFILL_BUCKET, PREFILL_GRAPH_MAX_TOKENS, BatchError, StepEntry, StepWorkspace, pad_decode_plan, pad_prefill_plan,
+                    plan_step, prefill_bucket, validate_entries)
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -60,6 +61,10 @@ class ModelRunner:
         self.vocab_size = self.spec.vocab_size
         # CUDA graphs of all-decode steps, keyed by the sizes that fix every launch of the step
         self.decode_graph = decode_graph and self.decoder.graph_safe
+        # Padding a prompt portion writes keys and values for tokens that do not exist: harmless where a
+        # request's next tokens overwrite them before they are read, which holds for caches that keep every
+        # key; not for windows (pages are given back by position) nor for state that every token updates.
+        self.prefill_graph = not self.manager.state_needs and all(g.window is None for g in self.manager.groups)
         self._graphs: dict[tuple, object] = {}
         self._graph_seen: dict[tuple, int] = {}
         self._graph_pool = None
@@ -103,10 +108,12 @@ class ModelRunner:
         self.manager.close(cache)
 
     def warm_up(self, prompt_tokens: tuple[int, ...] = (16, 64, 128, 256, 512, 1024, 2048, 4096, 8192),
-                decode_rows: tuple[int, ...] = (1, 2, 4, 8)) -> None:
+                decode_rows: tuple[int, ...] = (1, 2, 4, 8),
+                decode_contexts: tuple[int, ...] = (200, 400, 800, 1600, 3200)) -> None:
         """Runs throw-away steps so that what a first request would pay for is paid at load: the
-        library's kernels for prompt portions of several sizes (it loads them when first used) and
-        the captured graphs of small all-decode steps.  Sizes the pools cannot hold are left out;
+        library's kernels for prompt portions of several sizes (it loads them when first used), the
+        captured graphs of short prompt portions (every bucket) and those of small all-decode steps at
+        several context lengths.  Sizes the pools cannot hold are left out;
         every page and slot is given back."""
         free = min(self.manager.free_pages()) if self.manager.groups else 0
         page = self.manager.page_size
@@ -118,17 +125,35 @@ class ModelRunner:
                 self.step([StepEntry(rc, [0] * T, [T - 1])])
             finally:
                 self.close(rc)
+        if self.decode_graph and self.prefill_graph:
+            # a short prompt alone in its step replays a captured graph: seen, captured, replayed, per bucket
+            for T in range(PREFILL_BUCKET, PREFILL_GRAPH_MAX_TOKENS + 1, PREFILL_BUCKET):
+                if T > self.max_step_tokens or -(-T // page) > free or self.manager.slots.num_free < 1:
+                    continue
+                for _ in range(3):
+                    rc = self.open(("warm-up", "bucket", T))
+                    try:
+                        self.step([StepEntry(rc, [0] * T, [T - 1])])
+                    finally:
+                        self.close(rc)
+        # all-decode steps: per row count, and per width of the block table (it doubles with the context:
+        # requests that already hold 0, 200, 400, ... tokens, whose pages are taken but never written)
         for R in sorted(set(decode_rows)):
-            if R > self.manager.slots.num_free or R > free:
-                continue
-            rcs = [self.open(("warm-up", R, i)) for i in range(R)]
-            try:
-                self.step([StepEntry(rc, [0], [0]) for rc in rcs])       # the requests' first token
-                for _ in range(3):                                        # seen, captured, replayed
-                    self.step([StepEntry(rc, [0], [0]) for rc in rcs])
-            finally:
-                for rc in rcs:
-                    self.close(rc)
+            for held in (0,) + tuple(decode_contexts):
+                pages = -(-(held + 4) // page)
+                if R > self.manager.slots.num_free or R * pages > min(self.manager.free_pages()):
+                    continue
+                rcs = [self.open(("warm-up", R, held, i)) for i in range(R)]
+                try:
+                    for rc in rcs:
+                        if held:
+                            self.manager.extend(rc, held)
+                            self.manager.commit(rc, held)
+                    for _ in range(4):                                    # the first token; then seen, captured, replayed
+                        self.step([StepEntry(rc, [0], [0]) for rc in rcs])
+                finally:
+                    for rc in rcs:
+                        self.close(rc)
         torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------ the step
@@ -161,6 +186,15 @@ class ModelRunner:
             if graph:
                 # padded to a bucket of row counts, so that a few captured graphs serve every batch size
                 plan = pad_decode_plan(plan, self.manager.pad_pages, self.manager.pad_slot, self.step_arrays)
+            elif (self.decode_graph and self.prefill_graph and plan.num_rows == 1
+                  and plan.num_tokens <= PREFILL_GRAPH_MAX_TOKENS
+                  and prefill_bucket(plan.num_tokens) <= self.max_step_tokens):
+                # a short prompt portion alone in its step (a request that arrives at an idle engine): such
+                # a step is bound by the host that launches it, so it is padded to a bucket of token counts
+                # and replayed from a captured graph like the all-decode steps
+                padded = pad_prefill_plan(plan, self.manager.pad_pages, self.manager.page_size, self.step_arrays)
+                if self.workspace.layout(padded)[1] <= self.workspace.capacity:      # else: as it is, launch by launch
+                    graph, plan = True, padded
             inputs = self.workspace.upload(plan)
         except Exception:
             for e in entries:           # nothing was launched: the step holds nothing
@@ -197,7 +231,7 @@ class ModelRunner:
         seen = self._graph_seen.get(key, 0) + 1
         self._graph_seen[key] = seen
         logits = self.decoder.forward(inputs, self.caches)
-        if seen >= 2 and len(self._graphs) < 256:
+        if seen >= 2 and len(self._graphs) < 384:
             # Capturing launches nothing: the eager run above is this step's result (and the warm-up).
             before = ops.LAUNCHES
             graph = torch.cuda.CUDAGraph()

@@ -177,3 +177,37 @@ def test_a_step_that_cannot_be_uploaded_gives_its_pages_back():
     assert len(a.tables[0]) == 2
     m.close(a)
     m.assert_balanced()
+
+
+def test_a_prompt_portion_alone_is_padded_with_tokens_that_touch_only_its_own_slots_and_the_padding_page():
+    """The padded plan of a one-row step: the same row, longer; the added positions continue it; table
+    entries beyond the pages the request holds name the padding page; wanted places do not move."""
+    from acorninfer_b200.engine.batch import pad_prefill_plan, prefill_bucket
+    assert [prefill_bucket(n) for n in (2, 31, 32, 33, 100, 512)] == [32, 32, 32, 64, 128, 512]
+    P = 4
+    m = CacheManager({0: KVNeeds(2, 16, None)}, {}, 64, P, 16, dtype=torch.float32, device="cpu", allocate=False)
+    rc = m.open("a")
+    m.extend(rc, 9)
+    m.commit(rc, 9)                                      # 9 tokens held: pages 0..2, the third holding one token
+    m.extend(rc, 9 + 14)                                 # the step brings 14 more: 23 tokens, six pages
+    plan = plan_step([StepEntry(rc, list(range(1, 15)), [0, 13])], m, STEP_ARRAYS)
+    padded = pad_prefill_plan(plan, m.pad_pages, P, STEP_ARRAYS)
+    assert (padded.num_tokens, padded.num_rows, padded.num_logits) == (32, 1, 2) and not padded.all_decode
+    assert padded.token_ids[:14].tolist() == list(range(1, 15)) and not padded.token_ids[14:].any()
+    assert padded.positions.tolist() == list(range(9, 41)) and padded.row_start.tolist() == [0, 32]
+    assert padded.logit_tokens.tolist() == plan.logit_tokens.tolist() == [0, 13]
+    g, g0 = padded.groups[0], plan.groups[0]
+    assert g.kv_len.tolist() == [41] and g.max_kv_len == 41
+    held = len(rc.tables[0])
+    assert held == 6 and g.block_table[0, :held].tolist() == g0.block_table[0, :held].tolist() == list(rc.tables[0])
+    assert g.block_table[0, held:11].tolist() == [m.pad_pages[0]] * 5           # positions 24 .. 40: pages 6 .. 10
+    assert g.block_table.shape[1] >= 11
+    # a plan that is a bucket already, and a plan of several rows, stay as they are
+    rc2 = m.open("b")
+    m.extend(rc2, 32)
+    full = plan_step([StepEntry(rc2, [1] * 32, [31])], m, STEP_ARRAYS)
+    assert pad_prefill_plan(full, m.pad_pages, P, STEP_ARRAYS) is full
+    rc3 = m.open("c")
+    m.extend(rc3, 3)
+    two = plan_step([StepEntry(rc2, [1] * 32, []), StepEntry(rc3, [1, 2, 3], [2])], m, STEP_ARRAYS)
+    assert pad_prefill_plan(two, m.pad_pages, P, STEP_ARRAYS) is two

@@ -92,3 +92,51 @@ def test_a_step_too_large_for_the_workspace_is_refused_and_holds_nothing(tmp_pat
     for rc in [a] + others:
         runner.close(rc)
     runner.manager.assert_balanced()
+
+
+@pytest.mark.parametrize("tiny", [TINY_B, TINY_D], ids=["tiny_b", "tiny_d"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompts_replay_padded_graphs_and_what_the_padding_wrote_is_never_read(tmp_path, tiny, dtype):
+    """A prompt portion alone in its step is padded to a bucket of token counts and replayed from a
+    captured graph.  Three prompts of 45 tokens (bucket 64): the third replays; every logit against
+    the plain model.  The padding wrote keys and values at positions 45 .. 63 of the request's pages
+    (and into the padding page beyond them): the request then decodes 30 tokens through those
+    positions, and continues with a portion of 40 tokens that starts inside a page, all against the
+    plain model."""
+    import torch
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.engine.runner import ModelRunner
+    from tests.plain import model as plain
+    from tests.tiny import read_weights, sizes_of
+
+    d = make_model_dir(tmp_path / "m", tiny)
+    w, sizes, V = read_weights(d), sizes_of(tiny["cfg"]), tiny["cfg"].vocab_size
+    tol = 2e-5 if dtype == "float32" else 6e-2
+    runner = ModelRunner.from_model_dir(d, dtype=dtype, num_blocks=64, page_size=tiny["page_size"], max_requests=4)
+    assert runner.prefill_graph
+    seqs = [random_tokens(45 + 30 + 40, V, 70 + i) for i in range(3)]
+    rcs = []
+    for i, ids in enumerate(seqs):
+        rc = runner.open(i)
+        rcs.append(rc)
+        before = runner.graph_replays
+        got = runner.step([StepEntry(rc, ids[:45], list(range(45)))]).float().cpu().numpy()
+        assert (runner.graph_replays == before + 1) == (i == 2)          # seen, captured, replayed
+        want = plain.forward(sizes, w, ids[:45]).numpy()
+        assert np.abs(got - want).max() < tol, f"prompt {i}"
+    ids, rc = seqs[2], rcs[2]
+    want = plain.forward(sizes, w, ids).numpy()
+    for t in range(45, 75):                                              # through the slots the padding wrote
+        got = runner.step([StepEntry(rc, [ids[t]], [0])]).float().cpu().numpy()
+        assert np.abs(got[0] - want[t]).max() < tol, f"decoded token at {t}"
+    got = runner.step([StepEntry(rc, ids[75:115], list(range(40)))]).float().cpu().numpy()     # a padded portion that starts at 75
+    assert np.abs(got - want[75:115]).max() < tol
+    # the other requests' pages were not touched: they decode on as the plain model says
+    for i in (0, 1):
+        full = plain.forward(sizes, w, seqs[i][:46]).numpy()
+        got = runner.step([StepEntry(rcs[i], [seqs[i][45]], [0])]).float().cpu().numpy()
+        assert np.abs(got[0] - full[45]).max() < tol
+    for rc in rcs:
+        runner.close(rc)
+    runner.manager.assert_balanced()
+    torch.cuda.synchronize()
