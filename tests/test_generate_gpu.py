@@ -247,3 +247,23 @@ def test_preemption_and_recomputation_in_bfloat16_follow_the_plain_model(folders
     for i, p in zip(ids, prompts):
         assert len(eng.seqs[i].all_ids) == len(p) + 40
         assert follows_plain(sizes_of(cfg), w, p, eng.seqs[i].all_ids, 0.06), i
+
+
+def test_padded_prompt_graphs_change_no_token_in_float32(folders):
+    """One request at a time, so that every prompt (and every portion of a prompt cut by the budget) is
+    alone in its step: with graphs such steps are padded to 32 tokens and replayed, without graphs they run
+    as they are.  The float32 kernels give a row the same bits whatever else is in the step, so the two
+    engines must generate exactly the same tokens, greedy and sampled; lengths repeat so that buckets are
+    captured and replayed."""
+    from acorninfer_b200.engine.runner import ModelRunner
+    tiny, d, w = folders["b"]
+    cfg = tiny["cfg"]
+    lengths = (3, 17, 40, 33, 2, 31, 64, 17, 40, 5, 50, 33, 20, 61)
+    prompts = [random_tokens(n, cfg.vocab_size, 900 + i) for i, n in enumerate(lengths)]
+    out = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_model_dir(d, dtype="float32", num_blocks=40, page_size=8, max_requests=2, decode_graph=graphs)
+        out[graphs] = run_engine(runner, prompts, True, (), max_running=1, budget=48, watermark=1)[0]
+        if graphs:
+            assert runner.prefill_graph and runner.graph_replays > 20
+    assert out[False] == out[True]
