@@ -176,6 +176,29 @@ def time_prefill(runner, T: int, repeats: int, torch):
     return best
 
 
+def time_first_token(runner, T: int, torch) -> float:
+    """Milliseconds from a lone prompt of ``T`` host tokens to its first sampled token on the host (median of
+    seven after three warm-up prompts): the step is padded to a bucket of token counts and replayed from a graph."""
+    import statistics
+    from acorninfer_b200.engine.batch import StepEntry
+    from acorninfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(T)
+    z32, zf, z64 = (torch.zeros(1, dtype=d, device=runner.device) for d in (torch.int32, torch.float32, torch.int64))
+    one = torch.ones(1, dtype=torch.float32, device=runner.device)
+    times = []
+    for i in range(10):
+        toks = torch.randint(0, runner.vocab_size, (T,), generator=g).tolist()
+        rc = runner.open(f"ttft{T}_{i}")
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        logits = runner.step([StepEntry(rc, toks, [T - 1])])
+        tok = int(ops.sample(logits, zf, z32, one, z64, z64)[0].item())
+        times.append((time.perf_counter() - t0) * 1e3)
+        assert 0 <= tok < runner.vocab_size
+        runner.close(rc)
+    return statistics.median(times[3:])
+
+
 def time_e2e(runner, B: int, steps: int, warmup: int, ctx_end: int, torch):
     """The same metric through the public engine: ``Engine.submit`` then ``Engine.step()``;
     every step copies that step's token ids and tables from pinned host memory to the device and
@@ -603,7 +626,9 @@ def main() -> int:
         mid = PROMPT + (CONTEXT - PROMPT) // 2 + (args.steps + args.warmup) // 2
         for b in (1, 8, 64):
             points[f"decode_b{b}_ctx3072"] = round(time_decode(runner, sampler, b, args.steps, args.warmup, mid, torch)["tok_s"], 1)
-    pre_ms = time_prefill(runner, PROMPT, 3, torch)
+    pre_ms = time_prefill(runner, PROMPT, 6, torch)
+    if not args.skip_points:
+        points["first_token_ms_prompt128"] = round(time_first_token(runner, 128, torch), 3)
     e2e = time_e2e(runner, args.batch, args.steps, args.warmup, CONTEXT, torch)
     extra = {}
     if not args.skip_extra:
