@@ -31,8 +31,8 @@ from ..models.decoder import Decoder
 from ..registry import load_config, spec_for
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_state
-from .batch import (PREFILL_BUCKET, PREFILL_GRAPH_MAX_TOKENS, BatchError, StepEntry, StepWorkspace, pad_decode_plan, pad_prefill_plan,
-                    plan_step, prefill_bucket, validate_entries)
+from .batch import (PREFILL_GRAPH_MAX_TOKENS, BatchError, StepEntry, StepWorkspace, pad_decode_plan, pad_prefill_plan,
+                    plan_step, prefill_bucket, prefill_buckets, validate_entries)
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -127,7 +127,7 @@ class ModelRunner:
                 self.close(rc)
         if self.decode_graph and self.prefill_graph:
             # a short prompt alone in its step replays a captured graph: seen, captured, replayed, per bucket
-            for T in range(PREFILL_BUCKET, PREFILL_GRAPH_MAX_TOKENS + 1, PREFILL_BUCKET):
+            for T in prefill_buckets():
                 if T > self.max_step_tokens or -(-T // page) > free or self.manager.slots.num_free < 1:
                     continue
                 for _ in range(3):

@@ -183,7 +183,9 @@ def test_a_prompt_portion_alone_is_padded_with_tokens_that_touch_only_its_own_sl
     """The padded plan of a one-row step: the same row, longer; the added positions continue it; table
     entries beyond the pages the request holds name the padding page; wanted places do not move."""
     from acorninfer_b200.engine.batch import pad_prefill_plan, prefill_bucket
-    assert [prefill_bucket(n) for n in (2, 31, 32, 33, 100, 512)] == [32, 32, 32, 64, 128, 512]
+    from acorninfer_b200.engine.batch import prefill_buckets
+    assert [prefill_bucket(n) for n in (2, 31, 32, 33, 100, 512, 513, 600, 1024)] == [32, 32, 32, 64, 128, 512, 576, 640, 1024]
+    assert prefill_buckets() == list(range(32, 513, 32)) + list(range(576, 1025, 64))
     P = 4
     m = CacheManager({0: KVNeeds(2, 16, None)}, {}, 64, P, 16, dtype=torch.float32, device="cpu", allocate=False)
     rc = m.open("a")
