@@ -186,6 +186,20 @@ def test_a_prompt_of_600_tokens_with_gate_up_alone_on_the_paired_kernel(runner, 
         assert ran.get("qk_rope_kv") == LAYERS
         ops.raise_on_kernel_error()
     check(got, want, dtype_of(runner), "600 tokens whole")
+    # alone in its step, the prompt was padded to 640 tokens; the same shape again is captured, then replayed
+    # (the paired kernel inside a CUDA graph), and the padding's keys and values stay out of every result
+    replays = runner.graph_replays
+    for again in ("captured", "replayed"):
+        rc = runner.open("mid " + again)
+        got = runner.step([StepEntry(rc, ids, places)]).clone()
+        nxt = runner.step([StepEntry(rc, [ids[0]], [0])]).clone()      # a decoded token lands in a slot the padding wrote
+        runner.close(rc)
+        check(got, want, dtype_of(runner), "600 tokens, " + again)
+        if again == "captured":
+            want_next = plain64.logits(ids + [ids[0]], [600])
+        check(nxt, want_next, dtype_of(runner), "the token after, " + again)
+    assert runner.graph_replays >= replays + 1
+    ops.raise_on_kernel_error()
 
 
 def decode_case(runner, side, rows, prompt_lens, steps, seed):
