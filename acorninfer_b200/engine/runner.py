@@ -19,6 +19,7 @@ here it is one forward over the flat token batch.
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from pathlib import Path
 
 import torch
@@ -35,6 +36,9 @@ from .batch import (PREFILL_GRAPH_MAX_TOKENS, BatchError, StepEntry, StepWorkspa
                     plan_step, prefill_bucket, prefill_buckets, validate_entries)
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+MAX_GRAPHS = 384
 
 
 class ModelRunner:
@@ -65,8 +69,8 @@ class ModelRunner:
         # request's next tokens overwrite them before they are read, which holds for caches that keep every
         # key; not for windows (pages are given back by position) nor for state that every token updates.
         self.prefill_graph = not self.manager.state_needs and all(g.window is None for g in self.manager.groups)
-        self._graphs: dict[tuple, object] = {}
-        self._graph_seen: dict[tuple, int] = {}
+        self._graphs: OrderedDict[tuple, object] = OrderedDict()        # least recently replayed first
+        self._graph_seen: OrderedDict[tuple, int] = OrderedDict()
         self._graph_pool = None
         self.graph_kernel_launches = 0
         self.graph_replays = 0
@@ -215,7 +219,9 @@ class ModelRunner:
     # ------------------------------------------------------------------ captured decode steps
 
     def _decode_step(self, plan, inputs):
-        """An all-decode step: replayed from a CUDA graph once its shape has been seen twice.
+        """A step whose shape repeats (an all-decode step, or a short prompt portion alone, both padded to
+        buckets): replayed from a CUDA graph once its shape has been seen twice.  At most ``MAX_GRAPHS``
+        graphs are kept; the one replayed longest ago makes room for a new one.
 
         The step arrays were just uploaded to the addresses the graph reads (the address of every
         array the model reads is a function of the key), so a replay is this step.  The returned
@@ -223,15 +229,20 @@ class ModelRunner:
         key = self.workspace.shape_key(plan)
         entry = self._graphs.get(key)
         if entry is not None:
+            self._graphs.move_to_end(key)
             graph, logits, launches = entry
             graph.replay()
             self.graph_kernel_launches += launches
             self.graph_replays += 1
             return logits
-        seen = self._graph_seen.get(key, 0) + 1
+        seen = self._graph_seen.pop(key, 0) + 1
         self._graph_seen[key] = seen
+        if len(self._graph_seen) > 4 * MAX_GRAPHS:                       # shapes met once and never again
+            self._graph_seen.popitem(last=False)
         logits = self.decoder.forward(inputs, self.caches)
-        if seen >= 2 and len(self._graphs) < 384:
+        if seen >= 2:
+            if len(self._graphs) >= MAX_GRAPHS:                          # the shape replayed longest ago makes room
+                self._graphs.popitem(last=False)
             # Capturing launches nothing: the eager run above is this step's result (and the warm-up).
             before = ops.LAUNCHES
             graph = torch.cuda.CUDAGraph()

@@ -140,3 +140,32 @@ def test_short_prompts_replay_padded_graphs_and_what_the_padding_wrote_is_never_
         runner.close(rc)
     runner.manager.assert_balanced()
     torch.cuda.synchronize()
+
+
+def test_the_graph_replayed_longest_ago_makes_room(tmp_path, monkeypatch):
+    """With room for two graphs, a third shape evicts the one replayed longest ago; the evicted shape is
+    captured again when it comes back, and every step's logits stay what plain launches give."""
+    from acorninfer_b200.engine import runner as runner_module
+    from acorninfer_b200.engine.batch import StepEntry
+    d = make_model_dir(tmp_path / "m", TINY_B)
+    V = TINY_B["cfg"].vocab_size
+    monkeypatch.setattr(runner_module, "MAX_GRAPHS", 2)
+    plain = runner_module.ModelRunner.from_model_dir(d, dtype="float32", num_blocks=64, page_size=8, max_requests=8, decode_graph=False)
+    graphs = runner_module.ModelRunner.from_model_dir(d, dtype="float32", num_blocks=64, page_size=8, max_requests=8)
+    reqs = {r: [r.open(i) for i in range(3)] for r in (plain, graphs)}
+    for r in (plain, graphs):
+        for i, rc in enumerate(reqs[r]):
+            r.step([StepEntry(rc, random_tokens(4 + i, V, i), [])])
+    for step in range(18):
+        rows = (1, 2, 3)[(step // 3) % 3]                                 # three shapes in turn, three steps each
+        outs = []
+        for r in (plain, graphs):
+            logits = r.step([StepEntry(rc, [(5 * step + i) % V], [0]) for i, rc in enumerate(reqs[r][:rows])])
+            outs.append(logits.float().cpu().numpy().copy())
+        assert np.abs(outs[0] - outs[1]).max() <= 1e-6, step
+        assert len(graphs._graphs) <= 2
+    assert graphs.graph_replays >= 6                                      # the third step of every visit replays
+    for r in (plain, graphs):
+        for rc in reqs[r]:
+            r.close(rc)
+        r.manager.assert_balanced()
